@@ -82,6 +82,8 @@ def declare_runtime_api(lib: C.CDLL) -> None:
     f("bshmem_last_error", C.c_char_p, _VP)
     f("bshmem_get_error_record", _I, _VP, C.POINTER(ErrorRecord), _I)
     f("bshmem_status_string", C.c_char_p, _I)
+    f("bshmem_set_timeout_us", _I, _VP, _U64)
+    f("bshmem_get_timeout_us", _U64, _VP)
     f("bshmem_set_current", None, _VP)
     f("bshmem_get_current", _VP)
     f("bshmem_malloc", _VP, _VP, _SZ)

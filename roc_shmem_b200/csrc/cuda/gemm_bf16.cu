@@ -1,0 +1,108 @@
+// gemm_bf16.cu — stand-alone tcgen05 bf16 GEMM:  C[M,N] = A[M,K] · B[N,K]^T
+// (both operands K-major, i.e. activations times a torch Linear weight), fp32
+// accumulation in TMEM, bf16 output through TMA stores.  This is the compute core
+// that the fused all-gather→GEMM and GEMM→reduce-scatter kernels build on; it has
+// no counterpart in the reference, which contains no GEMM.
+#include "gemm_core.cuh"
+#include "tma_host.h"
+
+using namespace bshmem;
+using namespace bshmem::gemm;
+
+namespace {
+
+struct PlainParams {
+  CoreParams core;
+  CUtensorMap map_a, map_b, map_c;
+};
+
+struct PlainBf16 {
+  using Params = PlainParams;
+  static constexpr int kElemBytes = 2;
+  static constexpr uint32_t kIdesc = ptx::umma_idesc(1, 1, UMMA_M, UMMA_N);   // bf16 x bf16 -> fp32
+  static constexpr bool kWaitStoresPerTile = false;
+  __device__ static __forceinline__ const CoreParams& core(const Params& p) { return p.core; }
+  __device__ static __forceinline__ const CUtensorMap* map_a(const Params& p) { return &p.map_a; }
+  __device__ static __forceinline__ const CUtensorMap* map_b(const Params& p) { return &p.map_b; }
+  __device__ static __forceinline__ bool a_ready(const Params&, int, Guard&) { return true; }
+  __device__ static __forceinline__ void a_coords(const Params&, int m_blk, int* row) { *row = m_blk * BM; }
+  __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    ptx::umma_f16(d, a, b, idesc, acc);
+  }
+  __device__ static __forceinline__ uint32_t pack(uint32_t lo, uint32_t hi, const Params&, int, int) {
+    return pack_bf16(__uint_as_float(lo), __uint_as_float(hi));
+  }
+  __device__ static __forceinline__ void out_target(const Params& p, int row, int col, const CUtensorMap** map, int* x, int* y) {
+    *map = (row < p.core.M && col < p.core.N) ? &p.map_c : nullptr;
+    *x = col;
+    *y = row;
+  }
+  __device__ static __forceinline__ void tile_done(const Params&, int, int, int, int) {}
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_bf16_kernel(const __grid_constant__ PlainParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_mainloop<PlainBf16>(prm, smem_raw);
+}
+
+int* g_err_dev[64] = {};
+int g_sm_count[64] = {};
+
+int ensure_device_state(int dev) {
+  if (g_err_dev[dev]) return 0;
+  BSHMEM_CUDA_TRY(cudaMalloc(&g_err_dev[dev], sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaMemset(g_err_dev[dev], 0, sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* bshmem_gemm_last_error() { return host::last_error().c_str(); }
+
+// C = A · B^T.  A: [M, K] row-major (lda elements), B: [N, K] row-major (ldb), C: [M, N] (ldc), all bf16.
+// K, lda, ldb, ldc must be multiples of 8 and the bases 16-byte aligned (TMA).
+// max_ctas <= 0 uses one CTA per SM.  timeout_ms bounds every in-kernel wait.
+int bshmem_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                     void* stream, int max_ctas, int timeout_ms) {
+  if (M <= 0 || N <= 0 || K <= 0) { host::last_error() = "gemm: empty problem"; return 1; }
+  if ((K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8)) { host::last_error() = "gemm: K and leading dimensions must be multiples of 8"; return 1; }
+  int dev = 0;
+  BSHMEM_CUDA_TRY(cudaGetDevice(&dev));
+  int rc = ensure_device_state(dev);
+  if (rc) return rc;
+  PlainParams p;
+  p.core.M = M; p.core.N = N; p.core.K = K;
+  p.core.num_m_blocks = (M + BM - 1) / BM;
+  p.core.num_n_blocks = (N + BN - 1) / BN;
+  p.core.group_m = 8;
+  p.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  p.core.err = g_err_dev[dev];
+  rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, lda, BM, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, N, K, ldb, BN, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&p.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, M, N, ldc, 32, EPI_COLS);
+  if (rc) return rc;
+  int tiles = p.core.num_m_blocks * p.core.num_n_blocks;
+  int ctas = g_sm_count[dev];
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  gemm_bf16_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// Reads (and clears) the device error word of the current device: 0 = no bounded wait ran out.
+int bshmem_gemm_error_site(int clear) {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || !g_err_dev[dev]) return 0;
+  cudaMemcpy(&v, g_err_dev[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (clear && v) cudaMemset(g_err_dev[dev], 0, sizeof(int));
+  return v;
+}
+
+}  // extern "C"

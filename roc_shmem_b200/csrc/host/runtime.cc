@@ -135,6 +135,15 @@ const char* bshmem_status_string(int s) {
   }
 }
 
+int bshmem_set_timeout_us(bshmem_handle_t h, uint64_t timeout_us) {
+  CHECK_H(h);
+  if (timeout_us == 0) return BSHMEM_ERR_INVALID;
+  h->cfg.timeout_us = timeout_us;
+  h->backend->set_timeout_us(timeout_us);
+  return BSHMEM_OK;
+}
+uint64_t bshmem_get_timeout_us(bshmem_handle_t h) { return valid_handle(h) ? h->cfg.timeout_us : 0; }
+
 void bshmem_set_current(bshmem_handle_t h) { tls_current = h; }
 bshmem_handle_t bshmem_get_current(void) { return tls_current; }
 

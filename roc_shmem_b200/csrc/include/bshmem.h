@@ -58,6 +58,9 @@ int bshmem_global_exit(bshmem_handle_t h, int status);
 const char* bshmem_last_error(bshmem_handle_t h);
 int bshmem_get_error_record(bshmem_handle_t h, bshmem_error_record_t* out, int clear);
 const char* bshmem_status_string(int status);
+/* Bound of every blocking wait of this PE, host and device side. */
+int bshmem_set_timeout_us(bshmem_handle_t h, uint64_t timeout_us);
+uint64_t bshmem_get_timeout_us(bshmem_handle_t h);
 void bshmem_set_current(bshmem_handle_t h);     /* thread-local default handle */
 bshmem_handle_t bshmem_get_current(void);
 

@@ -1,0 +1,350 @@
+// bshmem_coll.cuh — device collectives over peer-mapped heaps.
+//
+// Every routine is a *block collective*: all threads of the calling block take
+// part, and the block identifies itself as channel `cta` of `ncta` so that a
+// host-launched kernel can stripe one collective over many CTAs (channel c of PE
+// i only ever synchronises with channel c of the other PEs).  A user kernel that
+// calls them roc_shmem-style from one block passes cta = 0, ncta = 1.
+//
+// NVSwitch gives every pair of GPUs full bandwidth, so all algorithms are direct
+// (one hop): barrier = all-to-all epoch flags; allreduce = one-shot pull for small
+// vectors, two-shot (reduce my slice from all peers, push the result to all peers)
+// for large ones; reduce-scatter = the first half of that; fcollect / alltoall =
+// direct pushes; broadcast = pull from the root.  With an NVLink multicast mapping
+// the allreduce can instead use multimem.ld_reduce / multimem.st.
+//
+// Parity: library/src/gpu_ib/context_ib_device_coll.cpp:30-120 (barriers),
+// context_ib_tmpl_device.hpp:120-307 (direct and ring allreduce, selection),
+// :455-519 (broadcast), :521-558 (alltoall), :836-876 (fcollect).  Unlike the
+// reference's reset-to-zero flags (context_ib_device_coll.cpp:38-52), barrier
+// flags carry a monotonically increasing epoch, which is safe for back-to-back
+// collectives; the log-step variants (Bruck, gcen) are not needed on a full mesh.
+#pragma once
+#include <type_traits>
+
+#include "bshmem_device.cuh"
+
+#ifdef __CUDACC__
+namespace bshmem {
+namespace coll {
+
+using dev::State;
+using dev::Team;
+
+__device__ __forceinline__ uint64_t* flag_addr(const State& s, int pe, int slot, int cta, int src_idx) {
+  return reinterpret_cast<uint64_t*>(s.heap_base[pe] + BSHMEM_OFF_FLAGS) +
+         ((size_t)slot * BSHMEM_MAX_COLL_CTAS + cta) * BSHMEM_MAX_PES + src_idx;
+}
+__device__ __forceinline__ uint64_t* epoch_addr(const State& s, int slot, int cta) {
+  return reinterpret_cast<uint64_t*>(s.heap_base[s.my_pe] + BSHMEM_OFF_EPOCHS) + (size_t)slot * BSHMEM_MAX_COLL_CTAS + cta;
+}
+
+// Active-set sync on the caller's pSync (single block per PE): members count in on the
+// first member's pSync[0]; that member resets the counter and releases everyone through
+// pSync[1], which each member resets itself, so both words end at BSHMEM_SYNC_VALUE.
+// (Same protocol as the flat barrier of context_ib_device_coll.cpp:30-55.)
+__device__ __forceinline__ int active_set_sync(const State& s, const Team& t) {
+  __shared__ int as_status;
+  if (threadIdx.x == 0) as_status = BSHMEM_OK;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    int root = dev::team_pe(t, 0);
+    unsigned long long* root_count = reinterpret_cast<unsigned long long*>(dev::ptr(s, t.psync, root));
+    atomicAdd_system(root_count, 1ull);
+    if (t.my_idx == 0) {
+      int rc = dev::wait_until<uint64_t>(s, reinterpret_cast<const uint64_t*>(t.psync), BSHMEM_CMP_EQ, (uint64_t)t.size,
+                                         BSHMEM_WHERE_BARRIER, -1);
+      if (rc == BSHMEM_OK) {
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(t.psync), "l"((uint64_t)BSHMEM_SYNC_VALUE) : "memory");
+        for (int i = 1; i < t.size; ++i) {
+          long* rel = dev::ptr(s, t.psync, dev::team_pe(t, i)) + 1;
+          asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(rel), "l"(1ull) : "memory");
+        }
+      } else {
+        as_status = rc;
+      }
+    } else {
+      int rc = dev::wait_until<uint64_t>(s, reinterpret_cast<const uint64_t*>(t.psync + 1), BSHMEM_CMP_EQ, 1ull,
+                                         BSHMEM_WHERE_BARRIER, root);
+      if (rc == BSHMEM_OK)
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(t.psync + 1), "l"((uint64_t)BSHMEM_SYNC_VALUE) : "memory");
+      else
+        as_status = rc;
+    }
+  }
+  __syncthreads();
+  int rc = as_status;
+  __syncthreads();
+  return rc;
+}
+
+// sync: every member's channel `cta` has arrived.  Does not complete RMA by itself,
+// but publishes the calling block's earlier stores (fence before the flag stores).
+// Returns BSHMEM_OK or BSHMEM_ERR_TIMEOUT (same value in every thread of the block).
+__device__ __forceinline__ int team_sync(const State& s, const Team& t, int cta = 0) {
+  if (t.slot < 0) return active_set_sync(s, t);
+  __shared__ int sync_status;
+  const int tid = threadIdx.x;
+  unsigned long long t0 = s.stats ? dev::timer() : 0;
+  if (tid == 0) sync_status = BSHMEM_OK;
+  __syncthreads();                       // all stores of the block precede the release below
+  uint64_t epoch = *epoch_addr(s, t.slot, cta) + 1;
+  if (tid < t.size) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    uint64_t* remote = flag_addr(s, dev::team_pe(t, tid), t.slot, cta, t.my_idx);
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(remote), "l"(epoch) : "memory");
+    const uint64_t* mine = flag_addr(s, s.my_pe, t.slot, cta, tid);
+    int rc = dev::wait_until<uint64_t>(s, mine, BSHMEM_CMP_GE, epoch, BSHMEM_WHERE_BARRIER, dev::team_pe(t, tid));
+    if (rc != BSHMEM_OK) sync_status = rc;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    *epoch_addr(s, t.slot, cta) = epoch;
+    if (s.stats) { dev::stat(s, BSHMEM_DSTAT_BARRIER); dev::stat(s, BSHMEM_DSTAT_BARRIER_NS, dev::timer() - t0); }
+  }
+  int rc = sync_status;
+  __syncthreads();
+  return rc;
+}
+// barrier = quiet + sync
+__device__ __forceinline__ int team_barrier(const State& s, const Team& t, int cta = 0) {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+  return team_sync(s, t, cta);
+}
+__device__ __forceinline__ int wg_barrier_all(const State& s) { return team_barrier(s, dev::team_world(s)); }
+__device__ __forceinline__ int wg_sync_all(const State& s) { return team_sync(s, dev::team_world(s)); }
+__device__ __forceinline__ int wg_team_sync(const State& s, const Team& t) { return team_sync(s, t); }
+
+// ---- element-wise reduction on 16-byte vectors ------------------------------------------------
+template <typename T> struct Acc { using type = T; };
+template <> struct Acc<__nv_bfloat16> { using type = float; };
+template <> struct Acc<__half> { using type = float; };
+
+template <typename A> __device__ __forceinline__ A apply(int op, A a, A b) {
+  if constexpr (std::is_floating_point<A>::value) {
+    switch (op) {
+      case BSHMEM_SUM: return a + b;
+      case BSHMEM_MIN: return b < a ? b : a;
+      case BSHMEM_MAX: return b > a ? b : a;
+      default: return a * b;
+    }
+  } else {
+    switch (op) {
+      case BSHMEM_SUM: return (A)(a + b);
+      case BSHMEM_MIN: return b < a ? b : a;
+      case BSHMEM_MAX: return b > a ? b : a;
+      case BSHMEM_PROD: return (A)(a * b);
+      case BSHMEM_AND: return (A)(a & b);
+      case BSHMEM_OR: return (A)(a | b);
+      default: return (A)(a ^ b);
+    }
+  }
+}
+template <typename T> __device__ __forceinline__ typename Acc<T>::type to_acc(T v) { return (typename Acc<T>::type)v; }
+template <> __device__ __forceinline__ float to_acc<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_acc<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_acc(typename Acc<T>::type v) { return (T)v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_acc<__half>(float v) { return __float2half_rn(v); }
+
+template <typename T> union Vec16 {
+  uint4 raw;
+  T e[16 / sizeof(T)];
+};
+
+// dst[i] = reduce over members k (in team order) of src_k[i], for i in [begin, end) elements;
+// the result goes to `ndst` destinations.  Vector body + scalar edges, striped over the block.
+template <typename T>
+__device__ __forceinline__ void reduce_range(int op, int nsrc, const T* const* srcs, int ndst, T* const* dsts,
+                                             size_t begin, size_t end) {
+  using A = typename Acc<T>::type;
+  constexpr int VE = 16 / sizeof(T);
+  const int tid = threadIdx.x, nth = blockDim.x;
+  // all sources and destinations share the symmetric offset, so one alignment check covers them
+  size_t vbeg = (begin + VE - 1) / VE * VE, vend = end / VE * VE;
+  bool aligned = ((uintptr_t)srcs[0] & 15) == 0 && ((uintptr_t)dsts[0] & 15) == 0;
+  if (!aligned || vbeg >= vend) { vbeg = vend = begin; }
+  for (size_t i = begin + tid; i < vbeg; i += nth) {
+    A acc = to_acc<T>(srcs[0][i]);
+    for (int k = 1; k < nsrc; ++k) acc = apply<A>(op, acc, to_acc<T>(srcs[k][i]));
+    for (int d = 0; d < ndst; ++d) dsts[d][i] = from_acc<T>(acc);
+  }
+  for (size_t v = vbeg / VE + tid; v < vend / VE; v += nth) {
+    Vec16<T> in;
+    A acc[VE];
+    in.raw = reinterpret_cast<const uint4*>(srcs[0])[v];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) acc[e] = to_acc<T>(in.e[e]);
+    for (int k = 1; k < nsrc; ++k) {
+      in.raw = reinterpret_cast<const uint4*>(srcs[k])[v];
+#pragma unroll
+      for (int e = 0; e < VE; ++e) acc[e] = apply<A>(op, acc[e], to_acc<T>(in.e[e]));
+    }
+    Vec16<T> out;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) out.e[e] = from_acc<T>(acc[e]);
+    for (int d = 0; d < ndst; ++d) reinterpret_cast<uint4*>(dsts[d])[v] = out.raw;
+  }
+  size_t tail = (vend > begin) ? vend : begin;
+  for (size_t i = tail + tid; i < end; i += nth) {
+    A acc = to_acc<T>(srcs[0][i]);
+    for (int k = 1; k < nsrc; ++k) acc = apply<A>(op, acc, to_acc<T>(srcs[k][i]));
+    for (int d = 0; d < ndst; ++d) dsts[d][i] = from_acc<T>(acc);
+  }
+}
+
+// Contiguous share of [0, n) for part `idx` of `parts`, in units of `gran` elements.
+__device__ __forceinline__ void split_range(size_t n, int parts, int idx, size_t gran, size_t* b, size_t* e) {
+  size_t units = (n + gran - 1) / gran;
+  size_t per = (units + parts - 1) / parts;
+  size_t ub = per * idx, ue = ub + per;
+  *b = ub * gran < n ? ub * gran : n;
+  *e = ue * gran < n ? ue * gran : n;
+}
+
+constexpr size_t kOneShotBytes = 64 * 1024;   // below this every PE reduces the whole vector itself
+
+// allreduce (`*_to_all`): dest and source are symmetric; dest may alias source.
+template <typename T>
+__device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
+                                           int cta = 0, int ncta = 1) {
+  const T* srcs[BSHMEM_MAX_PES];
+  T* dsts[BSHMEM_MAX_PES];
+  for (int k = 0; k < t.size; ++k) {
+    srcs[k] = dev::ptr(s, source, dev::team_pe(t, k));
+    dsts[k] = dev::ptr(s, dest, dev::team_pe(t, k));
+  }
+  int rc = team_sync(s, t, cta);          // every member's source is ready
+  if (rc != BSHMEM_OK) return rc;
+  constexpr size_t VE = 16 / sizeof(T);
+  bool one_shot = n * sizeof(T) <= kOneShotBytes && (const void*)dest != (const void*)source;
+  if (one_shot) {
+    size_t b, e;
+    split_range(n, ncta, cta, VE, &b, &e);
+    T* mine[1] = {dest};
+    reduce_range<T>(op, t.size, srcs, 1, mine, b, e);
+  } else {
+    // two-shot: I own slice my_idx; reduce it from everyone, push the result to everyone
+    size_t sb, se, b, e;
+    split_range(n, t.size, t.my_idx, VE, &sb, &se);
+    split_range(se - sb, ncta, cta, VE, &b, &e);
+    reduce_range<T>(op, t.size, srcs, t.size, dsts, sb + b, sb + e);
+  }
+  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  return team_barrier(s, t, cta);         // results delivered; sources reusable
+}
+
+// reduce-scatter: dest (n elements) = reduction of the members' source[my_idx*n : (my_idx+1)*n].
+template <typename T>
+__device__ __forceinline__ int team_reduce_scatter(const State& s, const Team& t, int op, T* dest, const T* source,
+                                                   size_t n, int cta = 0, int ncta = 1) {
+  const T* srcs[BSHMEM_MAX_PES];
+  for (int k = 0; k < t.size; ++k) srcs[k] = dev::ptr(s, source, dev::team_pe(t, k)) + (size_t)t.my_idx * n;
+  int rc = team_sync(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  size_t b, e;
+  split_range(n, ncta, cta, 16 / sizeof(T), &b, &e);
+  T* mine[1] = {dest};
+  // dest has its own offset; realign the vector path by handing in shifted bases
+  reduce_range<T>(op, t.size, srcs, 1, mine, b, e);
+  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  return team_barrier(s, t, cta);
+}
+
+// broadcast: the root's source lands in every other member's dest (the root's dest is untouched).
+__device__ __forceinline__ int team_broadcast(const State& s, const Team& t, void* dest, const void* source, size_t nbytes,
+                                              int root, int cta = 0, int ncta = 1) {
+  int rc = team_sync(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  if (t.my_idx != root) {
+    size_t b, e;
+    split_range(nbytes, ncta, cta, 16, &b, &e);
+    const char* src = dev::ptr(s, reinterpret_cast<const char*>(source), dev::team_pe(t, root));
+    dev::copy_bytes<dev::BLOCK>(reinterpret_cast<char*>(dest) + b, src + b, e - b);
+  }
+  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  return team_barrier(s, t, cta);
+}
+
+// fcollect (all-gather): my source lands in block my_idx of every member's dest.
+__device__ __forceinline__ int team_fcollect(const State& s, const Team& t, void* dest, const void* source, size_t nbytes,
+                                             int cta = 0, int ncta = 1) {
+  int rc = team_sync(s, t, cta);          // every member's dest may be overwritten
+  if (rc != BSHMEM_OK) return rc;
+  size_t b, e;
+  split_range(nbytes, ncta, cta, 16, &b, &e);
+  for (int k = 0; k < t.size; ++k) {
+    int peer_idx = (t.my_idx + k) % t.size;   // stagger the targets so the PEs do not gang up on one peer
+    char* d = dev::ptr(s, reinterpret_cast<char*>(dest), dev::team_pe(t, peer_idx)) + (size_t)t.my_idx * nbytes;
+    dev::copy_bytes<dev::BLOCK>(d + b, reinterpret_cast<const char*>(source) + b, e - b);
+  }
+  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  return team_barrier(s, t, cta);
+}
+
+// alltoall: block j of my source lands in block my_idx of member j's dest.
+__device__ __forceinline__ int team_alltoall(const State& s, const Team& t, void* dest, const void* source, size_t nbytes,
+                                             int cta = 0, int ncta = 1) {
+  int rc = team_sync(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  size_t b, e;
+  split_range(nbytes, ncta, cta, 16, &b, &e);
+  for (int k = 0; k < t.size; ++k) {
+    int j = (t.my_idx + k) % t.size;
+    char* d = dev::ptr(s, reinterpret_cast<char*>(dest), dev::team_pe(t, j)) + (size_t)t.my_idx * nbytes;
+    const char* sp = reinterpret_cast<const char*>(source) + (size_t)j * nbytes;
+    dev::copy_bytes<dev::BLOCK>(d + b, sp + b, e - b);
+  }
+  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  return team_barrier(s, t, cta);
+}
+
+// ---- NVLink-multicast (NVLS) allreduce: the switch reduces and broadcasts ----------------------
+// Works on 16-byte vectors of fp32 / bf16 sum only; the caller falls back otherwise.
+template <typename T>
+__device__ __forceinline__ int team_reduce_nvls(const State& s, const Team& t, T* dest, const T* source, size_t n,
+                                                int cta = 0, int ncta = 1) {
+  static_assert(std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value, "fp32 / bf16 only");
+  constexpr size_t VE = 16 / sizeof(T);
+  int rc = team_sync(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  size_t sb, se, b, e;
+  split_range(n, t.size, t.my_idx, VE, &sb, &se);
+  split_range(se - sb, ncta, cta, VE, &b, &e);
+  uint64_t soff = reinterpret_cast<const char*>(source) - s.heap_base[s.my_pe];
+  uint64_t doff = reinterpret_cast<char*>(dest) - s.heap_base[s.my_pe];
+  const char* mc_src = s.mc_base + soff;
+  char* mc_dst = s.mc_base + doff;
+  for (size_t v = (sb + b) / VE + threadIdx.x; v < (sb + e) / VE; v += blockDim.x) {
+    uint4 r;
+    if constexpr (std::is_same<T, float>::value) {
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_src + v * 16) : "memory");
+    } else {
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_src + v * 16) : "memory");
+    }
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_dst + v * 16), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+  }
+  return team_barrier(s, t, cta);
+}
+
+// roc_shmem-style names for single-block use ---------------------------------------------------------
+template <typename T> __device__ __forceinline__ int wg_to_all(const State& s, const Team& t, int op, T* dest, const T* src, size_t n) {
+  return team_reduce<T>(s, t, op, dest, src, n, 0, 1);
+}
+template <typename T> __device__ __forceinline__ int wg_broadcast(const State& s, const Team& t, T* dest, const T* src, size_t n, int root) {
+  return team_broadcast(s, t, dest, src, n * sizeof(T), root, 0, 1);
+}
+template <typename T> __device__ __forceinline__ int wg_fcollect(const State& s, const Team& t, T* dest, const T* src, size_t n) {
+  return team_fcollect(s, t, dest, src, n * sizeof(T), 0, 1);
+}
+template <typename T> __device__ __forceinline__ int wg_alltoall(const State& s, const Team& t, T* dest, const T* src, size_t n) {
+  return team_alltoall(s, t, dest, src, n * sizeof(T), 0, 1);
+}
+
+}  // namespace coll
+}  // namespace bshmem
+#endif  // __CUDACC__

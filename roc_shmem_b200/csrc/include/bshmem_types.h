@@ -157,6 +157,9 @@ enum {
   BSHMEM_WHERE_MUTEX = 10
 };
 
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
 static inline size_t bshmem_dtype_size(int dt) {
   switch (dt) {
     case BSHMEM_INT8: case BSHMEM_UINT8: return 1;

@@ -1,0 +1,295 @@
+"""NVLink backend front-end: one process per GPU, heaps mapped into every peer.
+
+Bring-up (the analogue of library/src/gpu_ib/backend_ib.cpp:70-111 and
+ipc_policy.cpp:34-111, with the store bootstrap in place of MPI):
+
+1. every PE creates its heap as a CUDA VMM allocation and exports a POSIX fd;
+2. fds are exchanged over Unix sockets, every PE maps every peer's heap into one
+   contiguous virtual range (``base + pe * heap_bytes``);
+3. optionally the allocations are bound to an NVLink multicast object (NVLS);
+4. the runtime handle is created on top of the mapped heap.
+
+If the driver refuses shareable VMM allocations the heap falls back to
+``cudaMalloc`` + ``cudaIpc`` handles, which travel through the store as bytes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+from . import _native
+from .bootstrap import Bootstrap
+from .config import Config
+from .cpu import native_config
+from .runtime import Runtime
+from .utils import dtypes as D
+from .utils.errors import ShmemError, raise_for_status
+
+_VP, _I, _U64 = C.c_void_p, C.c_int, C.c_uint64
+_declared = False
+
+
+class DevState(C.Structure):
+    """Mirror of bshmem_dev_state_t (passed by value to user kernels)."""
+    _fields_ = [("my_pe", C.c_int32), ("n_pes", C.c_int32), ("heap_bytes", C.c_uint64),
+                ("heap_base", C.c_void_p * 16), ("mc_base", C.c_void_p), ("err", C.c_void_p),
+                ("timeout_ns", C.c_ulonglong), ("stats", C.c_void_p), ("proxy", C.c_void_p),
+                ("debug", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+DSTAT_NAMES = ("put", "get", "put_signal", "p", "g", "amo", "fence", "quiet", "wait", "wait_ns", "barrier",
+               "barrier_ns", "coll", "bytes_put", "bytes_get", "timeouts", "proxy_ops")
+
+COLL_SYNC, COLL_BARRIER, COLL_BROADCAST, COLL_REDUCE, COLL_REDUCE_SCATTER, COLL_FCOLLECT, COLL_ALLTOALL = range(7)
+
+
+def cuda_lib() -> C.CDLL:
+    global _declared
+    lib = _native.load("libbshmem_cuda.so")
+    if not _declared:
+        _native.declare_runtime_api(lib)
+
+        def f(name, res, *args):
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, list(args)
+        f("bshmem_gpu_last_error", C.c_char_p)
+        f("bshmem_gpu_heap_create", _I, _I, _I, _U64, _I, _I, C.POINTER(_VP))
+        f("bshmem_gpu_heap_create_local_group", _I, _I, _U64, _I, C.POINTER(_VP))
+        f("bshmem_gpu_heap_export_fd", _I, _VP, C.POINTER(_I))
+        f("bshmem_gpu_heap_import_fd", _I, _VP, _I, _I)
+        f("bshmem_gpu_heap_export_ipc", _I, _VP, _VP)
+        f("bshmem_gpu_heap_import_ipc", _I, _VP, _I, _VP)
+        f("bshmem_gpu_multicast_supported", _I, _I)
+        f("bshmem_gpu_multicast_create", _I, _VP, C.POINTER(_I))
+        f("bshmem_gpu_multicast_import", _I, _VP, _I)
+        f("bshmem_gpu_multicast_add_device", _I, _VP)
+        f("bshmem_gpu_multicast_bind", _I, _VP)
+        f("bshmem_gpu_heap_destroy", _I, _VP)
+        f("bshmem_gpu_heap_bytes", _U64, _VP)
+        f("bshmem_gpu_init", _I, _VP, C.POINTER(_native.NativeConfig), _I, _I, C.POINTER(_VP))
+        f("bshmem_gpu_set_stream", _I, _VP, _VP)
+        f("bshmem_gpu_set_blocking", _I, _VP, _I)
+        f("bshmem_gpu_set_coll_ctas", _I, _VP, _I)
+        f("bshmem_gpu_set_nvls", _I, _VP, _I)
+        f("bshmem_gpu_get_state", _I, _VP, C.POINTER(DevState))
+        f("bshmem_gpu_check_error", _I, _VP)
+        f("bshmem_gpu_get_device_stats", _I, _VP, C.POINTER(_U64), _I)
+        f("bshmem_gpu_reset_device_stats", _I, _VP)
+        f("bshmem_gpu_rma_kernel", _I, _VP, _VP, _VP, _U64, _I, _I, _I, _I, _I)
+        f("bshmem_gpu_group_collective", _I, C.POINTER(_VP), _I, _I, _I, _I, _I, _I, _U64, _U64, _U64, _I)
+        f("bshmem_gpu_group_team_split", _I, C.POINTER(_VP), _I, _I, _I, _I, _I, C.POINTER(_I))
+        _declared = True
+    return lib
+
+
+class _CudaArray:
+    """Minimal __cuda_array_interface__ holder so torch can alias heap memory."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+def cuda_tensor_from_ptr(ptr: int, shape, dtype, device: torch.device) -> torch.Tensor:
+    n = 1
+    for s in shape:
+        n *= s
+    esz = torch.empty((), dtype=dtype).element_size()
+    nbytes = max(n * esz, 1)
+    raw = torch.as_tensor(_CudaArray(ptr, nbytes), device=device)
+    if n == 0:
+        return torch.empty(shape, dtype=dtype, device=device)
+    return raw[: n * esz].view(dtype).view(*shape)
+
+
+def _gpu_error(lib, what: str, status: int) -> None:
+    if status != 0:
+        msg = lib.bshmem_gpu_last_error()
+        raise_for_status(status, f"{what}: {msg.decode() if msg else ''}")
+
+
+class DeviceRuntime(Runtime):
+    """Runtime over the NVLink backend, plus the GPU-only knobs."""
+
+    backend = "device"
+
+    def __init__(self, lib, handle, device: torch.device, heap, own_heap: bool = True):
+        super().__init__(lib, handle,
+                         tensor_from_ptr=lambda p, shape, dtype: cuda_tensor_from_ptr(p, shape, dtype, device),
+                         device=device)
+        self.heap = heap
+
+    # stream-ordered mode: calls enqueue on `stream` and return; errors surface at quiet()
+    def set_stream(self, stream: Optional[torch.cuda.Stream]) -> None:
+        s = C.c_void_p(stream.cuda_stream) if stream is not None else C.c_void_p(0)
+        self._check(self.lib.bshmem_gpu_set_stream(self.h, s))
+
+    def set_blocking(self, blocking: bool) -> None:
+        self._check(self.lib.bshmem_gpu_set_blocking(self.h, int(blocking)))
+
+    def set_coll_ctas(self, n: int) -> None:
+        self._check(self.lib.bshmem_gpu_set_coll_ctas(self.h, n))
+
+    def set_nvls(self, on: bool) -> None:
+        self._check(self.lib.bshmem_gpu_set_nvls(self.h, int(on)))
+
+    def device_state(self) -> DevState:
+        st = DevState()
+        self._check(self.lib.bshmem_gpu_get_state(self.h, C.byref(st)))
+        return st
+
+    def check_error(self) -> None:
+        self._check(self.lib.bshmem_gpu_check_error(self.h))
+
+    def device_stats(self) -> dict:
+        arr = (C.c_uint64 * len(DSTAT_NAMES))()
+        self._check(self.lib.bshmem_gpu_get_device_stats(self.h, arr, len(DSTAT_NAMES)))
+        return dict(zip(DSTAT_NAMES, (int(v) for v in arr)))
+
+    def reset_device_stats(self) -> None:
+        self._check(self.lib.bshmem_gpu_reset_device_stats(self.h))
+
+    def rma_kernel(self, sym: torch.Tensor, local: torch.Tensor, pe: int, *, put: bool = True, scope: str = "block",
+                   ctas: int = 32, threads: int = 512, nbytes: Optional[int] = None) -> None:
+        """Device-initiated put/get striped over `ctas` CTAs (enqueued, not synchronised)."""
+        sc = {"thread": 0, "warp": 1, "block": 2}[scope]
+        n = nbytes if nbytes is not None else local.numel() * local.element_size()
+        self._check(self.lib.bshmem_gpu_rma_kernel(self.h, sym.data_ptr(), local.data_ptr(), n, pe, int(put), sc, ctas,
+                                                   threads))
+
+    def offset_of(self, t: torch.Tensor) -> int:
+        return t.data_ptr() - int(self.lib.bshmem_heap_base(self.h))
+
+
+def init_device_runtime(boot: Bootstrap, cfg: Config, device: Optional[int] = None, proxy: bool = False) -> DeviceRuntime:
+    if not torch.cuda.is_available():
+        raise ShmemError(7, "the device backend needs a CUDA device (use backend='cpu' otherwise)")
+    lib = cuda_lib()
+    if device is None:
+        device = int(os.environ.get("LOCAL_RANK", boot.rank)) % torch.cuda.device_count()
+    torch.cuda.set_device(device)
+    torch.cuda.init()
+    n = boot.world_size
+    heap = C.c_void_p()
+    mode = {"vmm": 0, "ipc": 1, "auto": 0}[cfg.heap_mode]
+    st = lib.bshmem_gpu_heap_create(boot.rank, n, cfg.heap_bytes, device, mode, C.byref(heap))
+    if st != 0 and cfg.heap_mode == "auto":
+        mode = 1
+        st = lib.bshmem_gpu_heap_create(boot.rank, n, cfg.heap_bytes, device, mode, C.byref(heap))
+    _gpu_error(lib, "heap_create", st)
+    # every PE must have picked the same mode
+    modes = boot.allgather(mode, tag="heap-mode") if n > 1 else [mode]
+    if len(set(modes)) != 1:
+        raise ShmemError(7, f"PEs disagree on the heap mode: {modes}")
+    if n > 1:
+        if mode == 0:
+            fd = C.c_int(-1)
+            _gpu_error(lib, "heap_export_fd", lib.bshmem_gpu_heap_export_fd(heap, C.byref(fd)))
+            fds = boot.exchange_fds([fd.value], tag="heap-fd")
+            for pe in range(n):
+                if pe != boot.rank:
+                    _gpu_error(lib, f"heap_import_fd(pe {pe})", lib.bshmem_gpu_heap_import_fd(heap, pe, fds[pe][0]))
+                    os.close(fds[pe][0])
+            os.close(fd.value)
+        else:
+            buf = (C.c_char * 64)()
+            _gpu_error(lib, "heap_export_ipc", lib.bshmem_gpu_heap_export_ipc(heap, buf))
+            handles = boot.allgather(bytes(buf), tag="heap-ipc")
+            for pe in range(n):
+                if pe != boot.rank:
+                    hb = (C.c_char * 64).from_buffer_copy(handles[pe])
+                    _gpu_error(lib, f"heap_import_ipc(pe {pe})", lib.bshmem_gpu_heap_import_ipc(heap, pe, hb))
+        boot.barrier("heap-mapped")
+    nvls_on = False
+    if n > 1 and mode == 0 and cfg.nvls in ("on", "auto"):
+        sup = boot.allgather(int(lib.bshmem_gpu_multicast_supported(device)), tag="nvls-sup")
+        if all(sup):
+            fd = C.c_int(-1)
+            if boot.rank == 0:
+                _gpu_error(lib, "multicast_create", lib.bshmem_gpu_multicast_create(heap, C.byref(fd)))
+            fds = boot.exchange_fds([fd.value] if boot.rank == 0 else [], tag="mc-fd")
+            if boot.rank != 0:
+                _gpu_error(lib, "multicast_import", lib.bshmem_gpu_multicast_import(heap, fds[0][0]))
+                os.close(fds[0][0])
+            else:
+                os.close(fd.value)
+            _gpu_error(lib, "multicast_add_device", lib.bshmem_gpu_multicast_add_device(heap))
+            boot.barrier("mc-added")
+            _gpu_error(lib, "multicast_bind", lib.bshmem_gpu_multicast_bind(heap))
+            boot.barrier("mc-bound")
+            nvls_on = True
+        elif cfg.nvls == "on":
+            raise ShmemError(8, "NVLink multicast requested but not supported on every PE")
+    nc = native_config(cfg)
+    nc.heap_bytes = lib.bshmem_gpu_heap_bytes(heap)
+    h = C.c_void_p()
+    _gpu_error(lib, "gpu_init", lib.bshmem_gpu_init(heap, C.byref(nc), cfg.coll_ctas, 1, C.byref(h)))
+    rt = DeviceRuntime(lib, h.value, torch.device("cuda", device), heap)
+    rt.config = cfg
+    rt.bootstrap = boot
+    rt.heap_mode = "vmm" if mode == 0 else "ipc"
+    rt.nvls = nvls_on
+    if nvls_on:
+        rt.set_nvls(True)
+    if n > 1:
+        boot.barrier("gpu-init")
+    if proxy:
+        from .proxy import attach_proxy
+        attach_proxy(rt)
+    return rt
+
+
+class LocalGroup:
+    """All PEs of a job inside ONE process on ONE GPU — for tests on a single
+    device.  Host RMA/atomics work per PE as usual; collectives and team splits
+    run for the whole group at once (one cooperative launch), because kernels
+    that wait on one another must never be separate launches on one GPU."""
+
+    def __init__(self, n_pes: int, heap_bytes: int = 64 << 20, device: int = 0, config: Optional[Config] = None):
+        self.lib = cuda_lib()
+        self.n_pes = n_pes
+        cfg = config or Config.from_env(backend="device", heap_bytes=heap_bytes)
+        torch.cuda.set_device(device)
+        torch.cuda.init()
+        heaps = (C.c_void_p * n_pes)()
+        _gpu_error(self.lib, "heap_create_local_group",
+                   self.lib.bshmem_gpu_heap_create_local_group(n_pes, cfg.heap_bytes, device, heaps))
+        self.heaps = list(heaps)
+        self.pes: list[DeviceRuntime] = []
+        nc = native_config(cfg)
+        nc.heap_bytes = self.lib.bshmem_gpu_heap_bytes(self.heaps[0])
+        for pe in range(n_pes):
+            h = C.c_void_p()
+            _gpu_error(self.lib, "gpu_init", self.lib.bshmem_gpu_init(self.heaps[pe], C.byref(nc), cfg.coll_ctas, 1, C.byref(h)))
+            rt = DeviceRuntime(self.lib, h.value, torch.device("cuda", device), self.heaps[pe])
+            rt.config = cfg
+            self.pes.append(rt)
+        self._handles = (C.c_void_p * n_pes)(*[rt.h.value for rt in self.pes])
+
+    def empty(self, shape, dtype) -> list[torch.Tensor]:
+        """The same symmetric allocation on every PE."""
+        return [rt.empty(shape, dtype, collective=False) for rt in self.pes]
+
+    def collective(self, kind: int, dests, srcs, count: int, *, dtype=None, op: int = 0, root: int = 0,
+                   team_slot: int = 0, ctas: int = 2) -> None:
+        d_off = self.pes[0].offset_of(dests[0]) if dests is not None else 0
+        s_off = self.pes[0].offset_of(srcs[0]) if srcs is not None else 0
+        code = D.code_of(dtype) if dtype is not None else 0
+        st = self.lib.bshmem_gpu_group_collective(self._handles, self.n_pes, team_slot, kind, code, op, root, d_off, s_off,
+                                                  count, ctas)
+        _gpu_error(self.lib, "group_collective", st)
+
+    def team_split(self, parent_slot: int, start: int, stride: int, size: int) -> list[int]:
+        out = (C.c_int * self.n_pes)()
+        _gpu_error(self.lib, "group_team_split",
+                   self.lib.bshmem_gpu_group_team_split(self._handles, self.n_pes, parent_slot, start, stride, size, out))
+        return list(out)
+
+    def close(self) -> None:
+        for rt in reversed(self.pes):
+            if not rt.finalized:
+                rt.finalize()
+        self.pes = []

@@ -1,0 +1,88 @@
+"""Tensor-parallel linear layers whose collective is fused into the GEMM kernel.
+
+``RowParallelLinear``  : y = reduce_scatter_M( x_shard @ W_shard.T )   (MLP down-projection)
+``ColumnParallelLinear``: y_shard = all_gather_M(x_shard) @ W_shard.T   (MLP gate/up projection)
+
+Both run hand-written sm_100a kernels (tcgen05 + TMEM + TMA) that move the tiles
+over NVLink peer memory from inside the GEMM; with one PE they reduce to the plain
+GEMM.  The reference has no such layer (it is a communication library only); these
+are the north-star workloads built on its device API shape.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops.gemm import gemm_bf16, gemm_error_site
+
+
+class RowParallelLinear:
+    """x: [M, K/P] (this rank's K shard) ; weight: [N, K/P] ; returns this rank's [M/P, N] rows of
+    sum over ranks of x_r @ w_r.T."""
+
+    def __init__(self, rt, in_features_per_rank: int, out_features: int, max_tokens: int,
+                 dtype: torch.dtype = torch.bfloat16):
+        if dtype != torch.bfloat16:
+            raise ValueError("bf16 only (see ops.gemm_fp8 for the block-scaled fp8 variant)")
+        self.rt = rt
+        self.P = rt.n_pes
+        self.K, self.N, self.M = in_features_per_rank, out_features, max_tokens
+        if self.M % self.P:
+            raise ValueError("token count must divide by the number of PEs")
+        dev = rt.device
+        self.weight = torch.empty((self.N, self.K), dtype=dtype, device=dev)
+        self.x_dev = torch.empty((self.M, self.K), dtype=dtype, device=dev)
+        self.metric_dev = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._launches = 0
+        if self.P == 1:
+            self.out = torch.empty((self.M, self.N), dtype=dtype, device=dev)
+            self.algorithm = "tcgen05 GEMM (256x256x64 tiles, 3-stage TMA ring, TMEM accumulators); 1 PE: no collective"
+            self._fused = None
+        else:
+            from ..ops.fused_tp import GemmReduceScatter
+            self._fused = GemmReduceScatter(rt, self.M, self.N, self.K)
+            self.out = self._fused.out
+            self.algorithm = self._fused.algorithm
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self._fused is None:
+            gemm_bf16(x, self.weight, self.out)
+            self._launches += 1
+            return self.out
+        self._launches += self._fused(x, self.weight)
+        return self.out
+
+    __call__ = forward
+
+    def step_from_host(self, x_host: torch.Tensor, metric_host: torch.Tensor) -> None:
+        """One serving-style step: pinned host activations -> device, layer, one scalar back."""
+        self.x_dev.copy_(x_host, non_blocking=True)
+        y = self.forward(self.x_dev)
+        torch.mean(y, dtype=torch.float32, out=self.metric_dev[0])
+        metric_host.copy_(self.metric_dev, non_blocking=True)
+
+    def reset_launch_count(self) -> None:
+        self._launches = 0
+
+    def launch_count(self) -> int:
+        return self._launches
+
+    def check(self) -> None:
+        site = gemm_error_site()
+        if site:
+            raise RuntimeError(f"a bounded in-kernel wait ran out (site {site})")
+        if self._fused is not None:
+            self._fused.check()
+
+
+def smoke_step(rt) -> None:
+    """Tiny forward of the flagship layer (used by the driver's smoke test)."""
+    layer = RowParallelLinear(rt, in_features_per_rank=256, out_features=512, max_tokens=512)
+    layer.weight.copy_((torch.randn(512, 256, device=rt.device) * 0.05).to(torch.bfloat16))
+    x = torch.randn(512, 256, device=rt.device).to(torch.bfloat16)
+    y = layer(x)
+    torch.cuda.synchronize()
+    layer.check()
+    ref = x.float() @ layer.weight.float().t()
+    assert (y.float() - ref).abs().max().item() < 0.05 * ref.abs().max().item() + 0.05
