@@ -1,0 +1,82 @@
+"""Single-GPU GEMM benchmark: the tcgen05 kernel against cuBLAS (torch.matmul) on
+the shapes of the tensor-parallel MLP, device-timed with CUDA events.
+
+    python -m roc_shmem_b200.bench.gemm_bench [--iters 30] [--small]
+
+Prints one JSON object per shape and a summary table; `--small` runs one small
+problem once (used for profiler captures, where a launch is replayed many times).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from ..ops.gemm import gemm_bf16, gemm_error_site
+
+SHAPES = [
+    ("down_proj_shard", 8192, 8192, 3584),
+    ("gate_up_shard", 8192, 7168, 8192),
+    ("square_8k", 8192, 8192, 8192),
+    ("square_4k", 4096, 4096, 4096),
+    ("moe_expert_up", 4096, 14336 * 2, 4096),
+]
+
+
+def time_fn(fn, iters: int, flush: torch.Tensor | None) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()            # 256 MiB write: evicts the 126 MB L2
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--max-ctas", type=int, default=0)
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    if args.small:
+        M, N, K = 2048, 2048, 2048
+        a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        b = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+        pad = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
+        pad.zero_()
+        out = gemm_bf16(a, b)
+        torch.cuda.synchronize()
+        print(json.dumps({"small": [M, N, K], "error_site": gemm_error_site()}))
+        return
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    for name, M, N, K in SHAPES:
+        a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ref = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ms_ours = time_fn(lambda: gemm_bf16(a, b, out, max_ctas=args.max_ctas), args.iters, flush)
+        ms_cublas = time_fn(lambda: torch.matmul(a, b.t(), out=ref), args.iters, flush)
+        err = (out.float() - ref.float()).abs().max().item()
+        fl = 2.0 * M * N * K
+        row = {"shape": name, "M": M, "N": N, "K": K, "ms_ours": round(ms_ours, 4), "ms_cublas": round(ms_cublas, 4),
+               "tflops_ours": round(fl / ms_ours / 1e9, 1), "tflops_cublas": round(fl / ms_cublas / 1e9, 1),
+               "ours_over_cublas": round(ms_cublas / ms_ours, 3), "max_abs_diff_vs_cublas": err,
+               "error_site": gemm_error_site()}
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+        del a, b, out, ref
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,481 @@
+// fused_tp.cu — tensor-parallel GEMMs with the collective inside the kernel (sm_100a).
+//
+//   GEMM → reduce-scatter (MLP down-projection):  every PE multiplies its K shard,
+//     out_q = sum_r (X_r · W_r^T)[rows of q].  The epilogue of each 256x256 tile TMA-stores
+//     the bf16 partial straight into the owner PE's staging slot over NVLink and bumps
+//     the tile's signal word there (putmem_signal semantics); tiles are ordered so that at
+//     any time the P ranks write to P different owners.  After its last tile every CTA
+//     turns into a reducer: it waits for the signals of the tiles it owns, sums the P
+//     partials in fp32 in a fixed order and writes the bf16 result.
+//
+//   all-gather → GEMM (gate/up projection):  X is row-sharded, out = gather(X) · W^T.
+//     The gathered buffer is symmetric; a PE's own rows already sit in it.  While the
+//     tensor core works, the epilogue warps of all CTAs pull the peers' rows piece by
+//     piece over NVLink (plain peer loads → local stores) in the order the tile schedule
+//     needs them and count arrivals per 256-row block; the TMA producer of a tile waits
+//     for its block's counter before loading A from *local* memory.
+//
+// No TMA load ever reads another GPU's memory, nothing uses cluster multicast, and
+// every wait (signals, ready/done flags, arrival counters, mbarriers) is bounded.
+// Staging is double-buffered by call parity and all flags are monotonic counters, so
+// back-to-back calls need no extra barrier.  No counterpart in the reference (it has
+// neither GEMMs nor fused collectives); the signalling follows its put + flag idiom
+// (library/src/gpu_ib/context_ib_tmpl_device.hpp:184-236).
+#include <vector>
+
+#include "../include/bshmem_device.cuh"
+#include "gemm_core.cuh"
+#include "tma_host.h"
+
+using namespace bshmem;
+using namespace bshmem::gemm;
+
+namespace {
+
+constexpr int kMaxPes = BSHMEM_MAX_PES;
+
+// =====================================================================================
+// GEMM -> reduce-scatter
+// =====================================================================================
+struct RsParams {
+  CoreParams core;
+  CUtensorMap map_a, map_b;
+  CUtensorMap map_out[kMaxPes];                 // owner q's staging slot of this rank: [rows_per_owner, N]
+  int P, my_rank, blocks_per_owner, rows_per_owner;
+  unsigned long long* sig_remote[kMaxPes];      // owner q's signal words, one per (row-block, n-block)
+  const unsigned long long* sig_local;
+  unsigned long long expect;                    // value of a tile's signal once all P partials of this call landed
+  const __nv_bfloat16* staging_local;           // [P][rows_per_owner][N] (this call's parity)
+  __nv_bfloat16* out;                           // [rows_per_owner, N]
+  long long ldo;
+};
+
+struct GemmRs : PolicyDefaults {
+  using Params = RsParams;
+  static constexpr int kElemBytes = 2;
+  static constexpr uint32_t kIdesc = ptx::umma_idesc(1, 1, UMMA_M, UMMA_N);
+  static constexpr bool kWaitStoresPerTile = true;   // the signal must follow the completed stores
+  __device__ static __forceinline__ const CoreParams& core(const Params& p) { return p.core; }
+  __device__ static __forceinline__ const CUtensorMap* map_a(const Params& p) { return &p.map_a; }
+  __device__ static __forceinline__ const CUtensorMap* map_b(const Params& p) { return &p.map_b; }
+  // Sub-round major: in sub-round s every rank visits the owners (me+1, me+2, ..., me) and computes
+  // row-block s of each, so the P ranks always target P different owners and all partials of an
+  // owner's row-block s have been sent when sub-round s ends.
+  __device__ static __forceinline__ void tile_coords(const Params& p, int tile, int* m_blk, int* n_blk) {
+    int per_sub = p.P * p.core.num_n_blocks;
+    int sub = tile / per_sub, rem = tile - sub * per_sub;
+    int step = rem / p.core.num_n_blocks;
+    *n_blk = rem - step * p.core.num_n_blocks;
+    int owner = (p.my_rank + 1 + step) % p.P;
+    *m_blk = owner * p.blocks_per_owner + sub;
+  }
+  __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * BM; }
+  __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    ptx::umma_f16(d, a, b, idesc, acc);
+  }
+  __device__ static __forceinline__ uint32_t pack(uint32_t lo, uint32_t hi, const Params&, int, int) {
+    return pack_bf16(__uint_as_float(lo), __uint_as_float(hi));
+  }
+  __device__ static __forceinline__ void out_target(const Params& p, int row, int col, const CUtensorMap** map, int* x, int* y) {
+    int owner = row / p.rows_per_owner;
+    *map = &p.map_out[owner];
+    *x = col;
+    *y = row - owner * p.rows_per_owner;
+  }
+  // The warp's TMA stores of this tile are complete: publish them and count one arrival on the owner.
+  __device__ static __forceinline__ void tile_done(const Params& p, int m_blk, int n_blk, int, int lane) {
+    if (lane == 0) {
+      int owner = m_blk / p.blocks_per_owner;
+      int idx = (m_blk - owner * p.blocks_per_owner) * p.core.num_n_blocks + n_blk;
+      ptx::fence_proxy_async_all();
+      ptx::fence_acq_rel_sys();
+      ptx::red_release_sys_add_u64(reinterpret_cast<uint64_t*>(p.sig_remote[owner] + idx), 1);
+    }
+  }
+  // Reduce the partials of the tiles this PE owns: 64-row slices of 256 columns, round-robin over CTAs,
+  // earliest sub-round first.
+  __device__ static __forceinline__ void tail(const Params& p, const Smem& L, Guard& g) {
+    const int num_n = p.core.num_n_blocks;
+    const int ntasks = p.blocks_per_owner * num_n * 4;
+    const long long N = p.core.N;
+    for (int task = blockIdx.x; task < ntasks; task += gridDim.x) {
+      int tile = task >> 2, slice = task & 3;
+      int blk = tile / num_n, n_blk = tile - blk * num_n;
+      if (threadIdx.x == 0)
+        *L.scratch() = wait_ge<true>(p.sig_local + tile, p.expect, g, ERR_PEER_SIGNAL) ? 1 : 0;
+      __syncthreads();
+      const bool ok = *L.scratch() != 0;
+      if (ok) {
+        const int r0 = blk * BM + slice * 64;
+        for (int v = threadIdx.x; v < 64 * (BN / 8); v += blockDim.x) {
+          int r = r0 + v / (BN / 8);
+          long long c = (long long)n_blk * BN + (v % (BN / 8)) * 8;
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+          for (int s = 0; s < kMaxPes; ++s) {
+            if (s < p.P) {
+              uint4 x = ptx::ld_relaxed_v4(p.staging_local + ((long long)s * p.rows_per_owner + r) * N + c);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 f = __bfloat1622float2(h[e]);
+                acc[2 * e] += f.x;
+                acc[2 * e + 1] += f.y;
+              }
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+          o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+          *reinterpret_cast<uint4*>(p.out + (long long)r * p.ldo + c) = o;
+        }
+      }
+      __syncthreads();
+    }
+  }
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_rs_kernel(const __grid_constant__ RsParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_mainloop<GemmRs>(prm, smem_raw);
+}
+
+// =====================================================================================
+// all-gather -> GEMM
+// =====================================================================================
+constexpr int kPieceBytes = 16384;
+
+struct AgParams {
+  CoreParams core;                              // M = all tokens, N = local output features
+  CUtensorMap map_a, map_b, map_c;              // A over the local gathered buffer
+  int P, my_rank, blocks_per_rank, pieces_per_row;
+  int pieces_per_block, pieces_per_src, total_pieces, pad;
+  unsigned long long row_bytes;
+  const char* xg_peer[kMaxPes];                 // every PE's gathered buffer as mapped here
+  char* xg_local;
+  unsigned long long* arrived;                  // local [num_m_blocks]: pieces landed (monotonic over calls)
+  unsigned long long* src_pulled;               // local [P]: pieces pulled per source (monotonic)
+  unsigned int* ticket;                         // local [2]: work counter of this call's parity
+  unsigned long long* ready_remote[kMaxPes];    // peer's ready[P]; this rank writes entry my_rank
+  const unsigned long long* ready_local;
+  unsigned long long* done_remote[kMaxPes];     // peer's done[P]; this rank writes entry my_rank
+  const unsigned long long* done_local;
+  unsigned long long call;
+};
+
+struct AgGemm : PolicyDefaults {
+  using Params = AgParams;
+  static constexpr int kElemBytes = 2;
+  static constexpr uint32_t kIdesc = ptx::umma_idesc(1, 1, UMMA_M, UMMA_N);
+  __device__ static __forceinline__ const CoreParams& core(const Params& p) { return p.core; }
+  __device__ static __forceinline__ const CUtensorMap* map_a(const Params& p) { return &p.map_a; }
+  __device__ static __forceinline__ const CUtensorMap* map_b(const Params& p) { return &p.map_b; }
+  // Source-major: first my own rows, then the rows of rank me+1, me+2, ... (the pull order).
+  __device__ static __forceinline__ void tile_coords(const Params& p, int tile, int* m_blk, int* n_blk) {
+    int per_src = p.blocks_per_rank * p.core.num_n_blocks;
+    int step = tile / per_src, rem = tile - step * per_src;
+    int src = (p.my_rank + step) % p.P;
+    *m_blk = src * p.blocks_per_rank + rem % p.blocks_per_rank;
+    *n_blk = rem / p.blocks_per_rank;
+  }
+  __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * BM; }
+  __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    ptx::umma_f16(d, a, b, idesc, acc);
+  }
+  __device__ static __forceinline__ uint32_t pack(uint32_t lo, uint32_t hi, const Params&, int, int) {
+    return pack_bf16(__uint_as_float(lo), __uint_as_float(hi));
+  }
+  __device__ static __forceinline__ void out_target(const Params& p, int row, int col, const CUtensorMap** map, int* x, int* y) {
+    *map = (row < p.core.M && col < p.core.N) ? &p.map_c : nullptr;
+    *x = col;
+    *y = row;
+  }
+  // One thread of CTA 0: recycle the other parity's ticket counter and tell every peer that this
+  // rank's rows are in place for this call (they were written by earlier work on the stream).
+  __device__ static __forceinline__ void prologue(const Params& p, Guard&) {
+    if (blockIdx.x != 0) return;
+    p.ticket[(p.call + 1) & 1] = 0;
+    ptx::fence_acq_rel_sys();
+    for (int q = 0; q < p.P; ++q)
+      if (q != p.my_rank) ptx::st_release_sys_u64(reinterpret_cast<uint64_t*>(p.ready_remote[q] + p.my_rank), p.call);
+  }
+  // The producer may load A rows of block m_blk once all of their pieces have landed locally.
+  __device__ static __forceinline__ bool a_ready(const Params& p, int m_blk, Guard& g) {
+    if (m_blk / p.blocks_per_rank == p.my_rank) return true;
+    if (!wait_ge<false>(p.arrived + m_blk, (unsigned long long)p.pieces_per_block * p.call, g, ERR_A_READY)) return false;
+    ptx::fence_proxy_async_all();     // generic-proxy stores (the pull) before async-proxy reads (TMA)
+    return true;
+  }
+  // A warp pulls one piece (<= 16 KiB of one row) of a peer's rows into the local gathered buffer.
+  __device__ static __forceinline__ bool idle_work(const Params& p, int, int lane, Guard& g) {
+    if (p.P == 1) return false;
+    unsigned int t = 0;
+    if (lane == 0) t = atomicAdd(&p.ticket[p.call & 1], 1u);
+    t = __shfl_sync(0xffffffffu, t, 0);
+    if (t >= (unsigned)p.total_pieces) return false;
+    int step = t / p.pieces_per_src, rem = t - step * p.pieces_per_src;
+    int blk_in_src = rem / p.pieces_per_block, piece = rem - blk_in_src * p.pieces_per_block;
+    int src = (p.my_rank + 1 + step) % p.P;
+    int row = piece / p.pieces_per_row, seg = piece - row * p.pieces_per_row;
+    int m_blk = src * p.blocks_per_rank + blk_in_src;
+    unsigned long long off = ((unsigned long long)m_blk * BM + row) * p.row_bytes + (unsigned long long)seg * kPieceBytes;
+    unsigned long long left = p.row_bytes - (unsigned long long)seg * kPieceBytes;
+    int nvec = (int)((left < (unsigned long long)kPieceBytes ? left : (unsigned long long)kPieceBytes) >> 4);
+    int ok = 1;
+    if (lane == 0) ok = wait_ge<true>(p.ready_local + src, p.call, g, ERR_PEER_READY) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return false;
+    const uint4* s4 = reinterpret_cast<const uint4*>(p.xg_peer[src] + off);
+    uint4* d4 = reinterpret_cast<uint4*>(p.xg_local + off);
+    int i = lane;
+    for (; i + 96 < nvec; i += 128) {     // four independent 16-byte peer loads in flight per lane
+      uint4 a = ptx::ld_relaxed_v4(s4 + i), b = ptx::ld_relaxed_v4(s4 + i + 32), c = ptx::ld_relaxed_v4(s4 + i + 64), d = ptx::ld_relaxed_v4(s4 + i + 96);
+      d4[i] = a; d4[i + 32] = b; d4[i + 64] = c; d4[i + 96] = d;
+    }
+    for (; i < nvec; i += 32) d4[i] = ptx::ld_relaxed_v4(s4 + i);
+    ptx::fence_proxy_async_all();
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence();
+      asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p.arrived + m_blk), "l"(1ull) : "memory");
+      unsigned long long pulled = atomicAdd(p.src_pulled + src, 1ull) + 1;
+      if (pulled == (unsigned long long)p.pieces_per_src * p.call) {
+        // everything of `src` is here: it may overwrite its rows once every PE said so
+        ptx::fence_acq_rel_sys();
+        ptx::st_release_sys_u64(reinterpret_cast<uint64_t*>(p.done_remote[src] + p.my_rank), p.call);
+      }
+    }
+    return true;
+  }
+  __device__ static __forceinline__ void epilogue_drain(const Params& p, int ew, int lane, Guard& g) {
+    while (idle_work(p, ew, lane, g)) {}
+  }
+  // Before the kernel ends, CTA 0 makes sure every peer has finished pulling this rank's rows.
+  __device__ static __forceinline__ void tail(const Params& p, const Smem&, Guard& g) {
+    if (blockIdx.x == 0 && threadIdx.x < p.P && (int)threadIdx.x != p.my_rank)
+      wait_ge<true>(p.done_local + threadIdx.x, p.call, g, ERR_PEER_DONE);
+  }
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_constant__ AgParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_mainloop<AgGemm>(prm, smem_raw);
+}
+
+// =====================================================================================
+// host side
+// =====================================================================================
+struct Plan {
+  int kind;                 // 0 = gemm->rs, 1 = ag->gemm
+  int device, sms;
+  bshmem_dev_state_t st;
+  int M, N, K;
+  unsigned long long call = 0;
+  int* err = nullptr;
+  // rs
+  char* staging_local = nullptr;   // symmetric, 2 parities
+  unsigned long long* sig_local = nullptr;
+  // ag
+  char* xg_local = nullptr;
+  unsigned long long* flags_local = nullptr;   // symmetric: ready[P] then done[P]
+  unsigned long long* arrived = nullptr;
+  unsigned long long* src_pulled = nullptr;
+  unsigned int* ticket = nullptr;
+};
+
+template <typename T> T* peer_ptr(const bshmem_dev_state_t& st, T* local, int pe) {
+  return reinterpret_cast<T*>(st.heap_base[pe] + (reinterpret_cast<char*>(local) - st.heap_base[st.my_pe]));
+}
+
+int common_init(Plan* p) {
+  BSHMEM_CUDA_TRY(cudaGetDevice(&p->device));
+  BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&p->sms, cudaDevAttrMultiProcessorCount, p->device));
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->err, sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaMemset(p->err, 0, sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+  return 0;
+}
+
+bool in_heap(const bshmem_dev_state_t& st, const void* p, uint64_t n) {
+  const char* c = static_cast<const char*>(p);
+  const char* b = st.heap_base[st.my_pe];
+  return c >= b && (uint64_t)(c - b) + n <= st.heap_bytes;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* bshmem_fused_last_error() { return host::last_error().c_str(); }
+
+// Bytes of symmetric memory the GEMM->RS plan needs: staging (2 parities x P slots x M/P x N bf16) and signals.
+uint64_t bshmem_fused_rs_staging_bytes(int M, int N) { return 2ull * (uint64_t)M * N * 2; }
+uint64_t bshmem_fused_rs_signal_bytes(int M, int N, int P) { return (uint64_t)(M / P / BM) * (N / BN) * 8; }
+
+int bshmem_fused_rs_plan(const bshmem_dev_state_t* st, int M, int N, int K, void* staging_local, void* sig_local, void** out) {
+  if (!st || !out) return 1;
+  int P = st->n_pes;
+  if (M % (P * BM) || N % BN || K % 8) {
+    host::last_error() = "gemm_rs: needs M % (P*256) == 0, N % 256 == 0, K % 8 == 0";
+    return 1;
+  }
+  if (!in_heap(*st, staging_local, bshmem_fused_rs_staging_bytes(M, N)) ||
+      !in_heap(*st, sig_local, bshmem_fused_rs_signal_bytes(M, N, P))) {
+    host::last_error() = "gemm_rs: staging / signal buffers must be symmetric allocations of the stated sizes";
+    return 4;
+  }
+  Plan* p = new Plan();
+  p->kind = 0; p->st = *st; p->M = M; p->N = N; p->K = K;
+  p->staging_local = static_cast<char*>(staging_local);
+  p->sig_local = static_cast<unsigned long long*>(sig_local);
+  int rc = common_init(p);
+  if (rc) { delete p; return rc; }
+  *out = p;
+  return 0;
+}
+
+// x: [M, K] bf16 (ldx), w: [N, K] bf16 (ldw), out: [M/P, N] bf16 (ldo): this PE's rows of the reduced product.
+int bshmem_fused_rs_run(void* plan, const void* x, int ldx, const void* w, int ldw, void* out, int ldo, void* stream,
+                        int timeout_ms, int max_ctas) {
+  Plan* p = static_cast<Plan*>(plan);
+  if (!p || p->kind != 0) return 1;
+  const int P = p->st.n_pes, me = p->st.my_pe;
+  const int rows = p->M / P;
+  p->call += 1;
+  RsParams prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.core.M = p->M; prm.core.N = p->N; prm.core.K = p->K;
+  prm.core.num_m_blocks = p->M / BM; prm.core.num_n_blocks = p->N / BN;
+  prm.core.group_m = 8;
+  prm.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  prm.core.err = p->err;
+  prm.P = P; prm.my_rank = me; prm.blocks_per_owner = rows / BM; prm.rows_per_owner = rows;
+  int rc = host::make_tmap_2d(&prm.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, p->M, p->K, ldx, BM, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&prm.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, p->N, p->K, ldw, BN, 64);
+  if (rc) return rc;
+  const uint64_t parity_bytes = (uint64_t)p->M * p->N * 2;          // P slots x rows x N
+  const uint64_t slot_bytes = (uint64_t)rows * p->N * 2;
+  char* stage_par = p->staging_local + (p->call & 1) * parity_bytes;
+  for (int q = 0; q < P; ++q) {
+    // my slot (index me) inside owner q's staging of this parity
+    char* dst = peer_ptr(p->st, stage_par, q) + (uint64_t)me * slot_bytes;
+    rc = host::make_tmap_2d(&prm.map_out[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dst, rows, p->N, p->N, 32, EPI_COLS);
+    if (rc) return rc;
+    prm.sig_remote[q] = peer_ptr(p->st, p->sig_local, q);
+  }
+  prm.sig_local = p->sig_local;
+  prm.expect = (unsigned long long)NUM_EPI_WARPS * P * p->call;
+  prm.staging_local = reinterpret_cast<const __nv_bfloat16*>(stage_par);
+  prm.out = static_cast<__nv_bfloat16*>(out);
+  prm.ldo = ldo;
+  int tiles = prm.core.num_m_blocks * prm.core.num_n_blocks;
+  int ctas = p->sms;
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  gemm_rs_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(prm);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// Symmetric memory of the AG->GEMM plan: the gathered activations [M, K] bf16 and 2*P flag words.
+uint64_t bshmem_fused_ag_flag_bytes(int P) { return 2ull * P * 8; }
+
+int bshmem_fused_ag_plan(const bshmem_dev_state_t* st, int M, int N, int K, void* xg_local, void* flags_local, void** out) {
+  if (!st || !out) return 1;
+  int P = st->n_pes;
+  if (M % (P * BM) || K % 8 || N % 8) {
+    host::last_error() = "ag_gemm: needs M % (P*256) == 0, K % 8 == 0, N % 8 == 0";
+    return 1;
+  }
+  if (!in_heap(*st, xg_local, (uint64_t)M * K * 2) || !in_heap(*st, flags_local, bshmem_fused_ag_flag_bytes(P))) {
+    host::last_error() = "ag_gemm: the gathered buffer and the flags must be symmetric allocations";
+    return 4;
+  }
+  Plan* p = new Plan();
+  p->kind = 1; p->st = *st; p->M = M; p->N = N; p->K = K;
+  p->xg_local = static_cast<char*>(xg_local);
+  p->flags_local = static_cast<unsigned long long*>(flags_local);
+  int rc = common_init(p);
+  if (rc) { delete p; return rc; }
+  int nblk = M / BM;
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->arrived, sizeof(unsigned long long) * nblk));
+  BSHMEM_CUDA_TRY(cudaMemset(p->arrived, 0, sizeof(unsigned long long) * nblk));
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->src_pulled, sizeof(unsigned long long) * kMaxPes));
+  BSHMEM_CUDA_TRY(cudaMemset(p->src_pulled, 0, sizeof(unsigned long long) * kMaxPes));
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->ticket, sizeof(unsigned int) * 2));
+  BSHMEM_CUDA_TRY(cudaMemset(p->ticket, 0, sizeof(unsigned int) * 2));
+  *out = p;
+  return 0;
+}
+
+// This PE's rows must already be in xg_local[my_pe * M/P : (my_pe+1) * M/P].  w: [N, K] (ldw), out: [M, N] (ldo).
+int bshmem_fused_ag_run(void* plan, const void* w, int ldw, void* out, int ldo, void* stream, int timeout_ms, int max_ctas) {
+  Plan* p = static_cast<Plan*>(plan);
+  if (!p || p->kind != 1) return 1;
+  const int P = p->st.n_pes, me = p->st.my_pe;
+  p->call += 1;
+  AgParams prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.core.M = p->M; prm.core.N = p->N; prm.core.K = p->K;
+  prm.core.num_m_blocks = p->M / BM; prm.core.num_n_blocks = (p->N + BN - 1) / BN;
+  prm.core.group_m = 8;
+  prm.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  prm.core.err = p->err;
+  prm.P = P; prm.my_rank = me; prm.blocks_per_rank = p->M / P / BM;
+  prm.row_bytes = (unsigned long long)p->K * 2;
+  prm.pieces_per_row = (int)((prm.row_bytes + kPieceBytes - 1) / kPieceBytes);
+  prm.pieces_per_block = BM * prm.pieces_per_row;
+  prm.pieces_per_src = prm.blocks_per_rank * prm.pieces_per_block;
+  prm.total_pieces = (P - 1) * prm.pieces_per_src;
+  int rc = host::make_tmap_2d(&prm.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p->xg_local, p->M, p->K, p->K, BM, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&prm.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, p->N, p->K, ldw, BN, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&prm.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, p->M, p->N, ldo, 32, EPI_COLS);
+  if (rc) return rc;
+  for (int q = 0; q < P; ++q) {
+    prm.xg_peer[q] = peer_ptr(p->st, p->xg_local, q);
+    prm.ready_remote[q] = peer_ptr(p->st, p->flags_local, q);
+    prm.done_remote[q] = peer_ptr(p->st, p->flags_local, q) + P;
+  }
+  prm.xg_local = p->xg_local;
+  prm.arrived = p->arrived;
+  prm.src_pulled = p->src_pulled;
+  prm.ticket = p->ticket;
+  prm.ready_local = p->flags_local;
+  prm.done_local = p->flags_local + P;
+  prm.call = p->call;
+  int tiles = prm.core.num_m_blocks * prm.core.num_n_blocks;
+  int ctas = p->sms;
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  ag_gemm_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(prm);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int bshmem_fused_error_site(void* plan, int clear) {
+  Plan* p = static_cast<Plan*>(plan);
+  int v = 0;
+  if (!p || !p->err) return 0;
+  cudaMemcpy(&v, p->err, sizeof(int), cudaMemcpyDeviceToHost);
+  if (clear && v) cudaMemset(p->err, 0, sizeof(int));
+  return v;
+}
+
+int bshmem_fused_destroy(void* plan) {
+  Plan* p = static_cast<Plan*>(plan);
+  if (!p) return 0;
+  cudaFree(p->err);
+  if (p->arrived) cudaFree(p->arrived);
+  if (p->src_pulled) cudaFree(p->src_pulled);
+  if (p->ticket) cudaFree(p->ticket);
+  delete p;
+  return 0;
+}
+
+}  // extern "C"

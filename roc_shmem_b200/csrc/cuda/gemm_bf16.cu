@@ -16,16 +16,17 @@ struct PlainParams {
   CUtensorMap map_a, map_b, map_c;
 };
 
-struct PlainBf16 {
+struct PlainBf16 : PolicyDefaults {
   using Params = PlainParams;
   static constexpr int kElemBytes = 2;
   static constexpr uint32_t kIdesc = ptx::umma_idesc(1, 1, UMMA_M, UMMA_N);   // bf16 x bf16 -> fp32
-  static constexpr bool kWaitStoresPerTile = false;
   __device__ static __forceinline__ const CoreParams& core(const Params& p) { return p.core; }
   __device__ static __forceinline__ const CUtensorMap* map_a(const Params& p) { return &p.map_a; }
   __device__ static __forceinline__ const CUtensorMap* map_b(const Params& p) { return &p.map_b; }
-  __device__ static __forceinline__ bool a_ready(const Params&, int, Guard&) { return true; }
-  __device__ static __forceinline__ void a_coords(const Params&, int m_blk, int* row) { *row = m_blk * BM; }
+  __device__ static __forceinline__ void tile_coords(const Params& p, int tile, int* m_blk, int* n_blk) {
+    raster_coords(p.core, tile, m_blk, n_blk);
+  }
+  __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * BM; }
   __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
     ptx::umma_f16(d, a, b, idesc, acc);
   }
@@ -37,7 +38,6 @@ struct PlainBf16 {
     *x = col;
     *y = row;
   }
-  __device__ static __forceinline__ void tile_done(const Params&, int, int, int, int) {}
 };
 
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_bf16_kernel(const __grid_constant__ PlainParams prm) {

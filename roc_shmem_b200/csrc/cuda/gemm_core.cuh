@@ -3,9 +3,9 @@
 // in tensor memory.
 //
 // One CTA per SM owns a 256x256 output tile at a time:
-//   warp 0      TMA producer: A (256x64) and B (256x64) stages, 128-byte swizzle,
-//               3-stage ring of 64 KiB, plain (non-multicast) tiled bulk loads
-//   warp 1      MMA issuer: per 64-wide k-block 2 x 4 tcgen05.mma (M128,N256,K16);
+//   warp 0      TMA producer: A (256 rows) and B (256 rows) stages of 128 bytes of K,
+//               128-byte swizzle, 3-stage ring of 64 KiB, plain (non-multicast) tiled loads
+//   warp 1      MMA issuer: per k-block 2 x 4 tcgen05.mma (M128,N256,K 32 bytes);
 //               rows 0-127 accumulate in TMEM columns 0-255, rows 128-255 in 256-511
 //   warps 2-9   epilogue: tcgen05.ld -> convert -> swizzled smem -> TMA store
 // A 256x256 tile needs 128 FLOP per byte of smem fill, which keeps the L2->SM
@@ -13,10 +13,12 @@
 // price is that both accumulators are busy, so the epilogue of a tile only
 // overlaps the next tile's TMA prefetch, not its MMAs.
 //
-// The main loop is parameterised by a Policy so that the fused
-// compute+collective kernels reuse it: the policy decides when an A row-block
-// may be loaded (all-gather → GEMM waits for the chunk's arrival signal) and
-// where an output chunk goes (GEMM → reduce-scatter stores into the owner PE).
+// The main loop is parameterised by a Policy so that the fused compute+collective
+// kernels reuse it.  The policy decides the tile order, when an A row-block may be
+// loaded (all-gather → GEMM waits for the block's arrival counter), where an output
+// chunk goes (GEMM → reduce-scatter stores into the owner PE's memory), what the
+// epilogue warps do while they wait for the tensor core (pull peer data), and what
+// the whole CTA does after its last tile (reduce the partials that arrived).
 //
 // Every wait is bounded by a %globaltimer deadline; on expiry the CTA records a
 // site code in the error word, lets in-flight copies land, frees its TMEM and
@@ -34,7 +36,7 @@ constexpr int UMMA_M = 128, UMMA_N = 256;
 constexpr int UMMA_K_BYTES = 32;                  // K extent of one tcgen05.mma in bytes (16 bf16 / 32 fp8)
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 32 * (2 + NUM_EPI_WARPS);
-constexpr int EPI_COLS = 64;                       // columns per epilogue chunk (128 B of bf16)
+constexpr int EPI_COLS = 64;                      // columns per epilogue chunk (128 B of bf16)
 constexpr uint32_t A_STAGE_BYTES = BM * BK_BYTES;
 constexpr uint32_t B_STAGE_BYTES = BN * BK_BYTES;
 constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -45,7 +47,7 @@ constexpr uint32_t TMEM_COLS = 512;
 
 enum ErrSite : int {
   ERR_NONE = 0, ERR_PRODUCER_EMPTY = 101, ERR_MMA_FULL = 102, ERR_MMA_TMEM_EMPTY = 103, ERR_EPI_TMEM_FULL = 104,
-  ERR_A_READY = 105, ERR_PEER_SIGNAL = 106
+  ERR_A_READY = 105, ERR_PEER_SIGNAL = 106, ERR_PEER_READY = 107, ERR_PEER_DONE = 108
 };
 
 struct CoreParams {
@@ -82,9 +84,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Guard& 
   return true;
 }
 
+// Bounded wait until *p >= target (acquire at gpu or system scope).
+template <bool kSys>
+__device__ __forceinline__ bool wait_ge(const unsigned long long* p, unsigned long long target, Guard& g, int site) {
+  unsigned long long t0 = 0;
+  uint32_t it = 0;
+  while (true) {
+    unsigned long long v;
+    if (kSys) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    else asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    if (v >= target) return true;
+    if ((++it & 0xF) == 0) {
+      if (*g.abort_flag) return false;
+      unsigned long long now = ptx::globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > g.timeout_ns) return guard_fail(g, site);
+      __nanosleep(100);
+    }
+  }
+}
+
 // Grouped raster: consecutive tile ids walk down `group_m` row-blocks before
 // moving to the next column-block, so concurrently running CTAs share A and B.
-__device__ __forceinline__ void tile_coords(const CoreParams& p, int tile, int* m_blk, int* n_blk) {
+__device__ __forceinline__ void raster_coords(const CoreParams& p, int tile, int* m_blk, int* n_blk) {
   int per_group = p.group_m * p.num_n_blocks;
   int g = tile / per_group;
   int first_m = g * p.group_m;
@@ -94,29 +116,33 @@ __device__ __forceinline__ void tile_coords(const CoreParams& p, int tile, int* 
   *n_blk = in_g / rows;
 }
 
-struct SmemLayout {
-  uint32_t a[STAGES], b[STAGES], epi[NUM_EPI_WARPS];
-  uint32_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
-  uint32_t tmem_slot;
-  volatile int* abort_flag;
+// Shared-memory carve-up (all addresses are shared-window byte addresses).
+struct Smem {
+  uint32_t base;        // 1024-byte aligned
+  uint8_t* gen;         // generic pointer to the same byte
+  __device__ __forceinline__ uint32_t a(int s) const { return base + s * STAGE_BYTES; }
+  __device__ __forceinline__ uint32_t b(int s) const { return base + s * STAGE_BYTES + A_STAGE_BYTES; }
+  __device__ __forceinline__ uint32_t epi(int w) const { return base + STAGES * STAGE_BYTES + w * EPI_BUF_BYTES; }
+  __device__ __forceinline__ uint32_t bars() const { return base + SMEM_TILES; }
+  __device__ __forceinline__ uint32_t full(int s) const { return bars() + 8 * s; }
+  __device__ __forceinline__ uint32_t empty(int s) const { return bars() + 8 * (STAGES + s); }
+  __device__ __forceinline__ uint32_t tmem_full(int h) const { return bars() + 8 * (2 * STAGES + h); }
+  __device__ __forceinline__ uint32_t tmem_empty(int h) const { return bars() + 8 * (2 * STAGES + 2 + h); }
+  __device__ __forceinline__ uint32_t tmem_slot() const { return bars() + 8 * (2 * STAGES + 4); }
+  __device__ __forceinline__ volatile int* abort_flag() const {
+    return reinterpret_cast<volatile int*>(gen + SMEM_TILES + 8 * (2 * STAGES + 4) + 8);
+  }
+  // 16 bytes of policy scratch (e.g. a broadcast slot for the tail phase)
+  __device__ __forceinline__ volatile int* scratch() const {
+    return reinterpret_cast<volatile int*>(gen + SMEM_TILES + 8 * (2 * STAGES + 4) + 16);
+  }
 };
 
-__device__ __forceinline__ SmemLayout carve_smem(uint8_t* raw) {
-  SmemLayout L;
-  uint32_t base = (ptx::smem_u32(raw) + 1023u) & ~1023u;
-  uint8_t* gen = raw + (base - ptx::smem_u32(raw));
-  for (int s = 0; s < STAGES; ++s) {
-    L.a[s] = base + s * STAGE_BYTES;
-    L.b[s] = L.a[s] + A_STAGE_BYTES;
-  }
-  uint32_t e = base + STAGES * STAGE_BYTES;
-  for (int w = 0; w < NUM_EPI_WARPS; ++w) L.epi[w] = e + w * EPI_BUF_BYTES;
-  uint32_t bars = base + SMEM_TILES;
-  for (int s = 0; s < STAGES; ++s) { L.full[s] = bars + 8 * s; L.empty[s] = bars + 8 * (STAGES + s); }
-  L.tmem_full[0] = bars + 8 * (2 * STAGES); L.tmem_full[1] = L.tmem_full[0] + 8;
-  L.tmem_empty[0] = L.tmem_full[1] + 8;     L.tmem_empty[1] = L.tmem_empty[0] + 8;
-  L.tmem_slot = L.tmem_empty[1] + 8;
-  L.abort_flag = reinterpret_cast<volatile int*>(gen + SMEM_TILES + 8 * (2 * STAGES + 4) + 8);
+__device__ __forceinline__ Smem carve_smem(uint8_t* raw) {
+  Smem L;
+  uint32_t r = ptx::smem_u32(raw);
+  L.base = (r + 1023u) & ~1023u;
+  L.gen = raw + (L.base - r);
   return L;
 }
 
@@ -126,44 +152,60 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Policy contract (all static __device__, P::Params is passed by value to the kernel):
-//   const CoreParams& core(const Params&)
-//   const CUtensorMap* map_a(const Params&), map_b(const Params&)
-//   bool a_ready(const Params&, int m_blk, Guard&)               producer lane, before a tile's first A load
-//   void a_coords(const Params&, int m_blk, int* row)            row coordinate of the A block in map_a
-//   void out_target(const Params&, int row, int col, const CUtensorMap** map, int* x, int* y)
-//        where the 32x64 chunk whose first element is C[row, col] is stored
-//   float scale(...) not used here
-//   void tile_done(const Params&, int m_blk, int n_blk, int epi_warp, int lane)   after the warp's stores were issued
-//   static constexpr bool kWaitStoresPerTile     tile_done needs the warp's stores complete and visible
+// Defaults a policy can inherit.
+struct PolicyDefaults {
+  static constexpr bool kWaitStoresPerTile = false;
+  template <class Params> __device__ static __forceinline__ bool a_ready(const Params&, int, Guard&) { return true; }
+  template <class Params> __device__ static __forceinline__ void tile_done(const Params&, int, int, int, int) {}
+  // work for an epilogue warp while the tensor core is busy; false = nothing to do
+  template <class Params> __device__ static __forceinline__ bool idle_work(const Params&, int, int, Guard&) { return false; }
+  // after an epilogue warp's last tile
+  template <class Params> __device__ static __forceinline__ void epilogue_drain(const Params&, int, int, Guard&) {}
+  // whole CTA, after all roles have finished (before TMEM is released)
+  template <class Params> __device__ static __forceinline__ void tail(const Params&, const Smem&, Guard&) {}
+  // one-time work of one thread of the CTA at kernel start
+  template <class Params> __device__ static __forceinline__ void prologue(const Params&, Guard&) {}
+};
+
+// Policy contract (static __device__ members; P::Params is the kernel's by-value parameter):
+//   core(prm) -> const CoreParams&        map_a(prm), map_b(prm) -> const CUtensorMap*
+//   kElemBytes, kIdesc                    mma(d_tmem, adesc, bdesc, idesc, accumulate)
+//   tile_coords(prm, tile, &m_blk, &n_blk)
+//   a_ready(prm, m_blk, guard)            producer lane, before a tile's first A load
+//   a_row(prm, m_blk) -> int              row coordinate of the A block in map_a
+//   pack(lo_bits, hi_bits, prm, row, col) -> uint32   two accumulators -> one output word
+//   out_target(prm, row, col, &map, &x, &y)  where the 32x64 chunk starting at C[row, col] goes
+//   tile_done(prm, m_blk, n_blk, epi_warp, lane)  after the warp's stores (complete if kWaitStoresPerTile)
+//   idle_work / epilogue_drain / tail / prologue as in PolicyDefaults
 template <class P>
 __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uint8_t* smem_raw) {
   const CoreParams& cp = P::core(prm);
-  SmemLayout L = carve_smem(smem_raw);
+  const Smem L = carve_smem(smem_raw);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = cp.num_m_blocks * cp.num_n_blocks;
   constexpr int BK = BK_BYTES / P::kElemBytes;   // k-block in elements
   const int num_kb = (cp.K + BK - 1) / BK;
-  Guard g{cp.err, L.abort_flag, cp.timeout_ns};
+  Guard g{cp.err, L.abort_flag(), cp.timeout_ns};
 
   if (threadIdx.x == 0) {
-    *L.abort_flag = 0;
-    for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(L.full[s], 1); ptx::mbar_init(L.empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(L.tmem_full[a], 1); ptx::mbar_init(L.tmem_empty[a], NUM_EPI_WARPS / 2); }
+    *L.abort_flag() = 0;
+    for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(L.full(s), 1); ptx::mbar_init(L.empty(s), 1); }
+    for (int h = 0; h < 2; ++h) { ptx::mbar_init(L.tmem_full(h), 1); ptx::mbar_init(L.tmem_empty(h), NUM_EPI_WARPS / 2); }
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(P::map_a(prm));
     ptx::prefetch_tensormap(P::map_b(prm));
   }
   if (warp == 1) {
-    ptx::tmem_alloc(L.tmem_slot, TMEM_COLS);
+    ptx::tmem_alloc(L.tmem_slot(), TMEM_COLS);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   uint32_t tmem_base;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(L.tmem_slot));
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(L.tmem_slot()));
+  if (threadIdx.x == 64) P::prologue(prm, g);      // first epilogue warp's lane 0
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -172,15 +214,14 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(cp, tile, &m_blk, &n_blk);
-        if (!P::a_ready(prm, m_blk, g)) { ok = false; break; }
-        int a_row;
-        P::a_coords(prm, m_blk, &a_row);
+        P::tile_coords(prm, tile, &m_blk, &n_blk);
+        if (!P::a_ready(prm, m_blk, g)) break;
+        const int a_row = P::a_row(prm, m_blk);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(L.empty[s], ph ^ 1, g, ERR_PRODUCER_EMPTY)) { ok = false; break; }
-          ptx::mbar_arrive_expect_tx(L.full[s], STAGE_BYTES);
-          ptx::tma_load_2d(L.a[s], P::map_a(prm), L.full[s], kb * BK, a_row);
-          ptx::tma_load_2d(L.b[s], P::map_b(prm), L.full[s], kb * BK, n_blk * BN);
+          if (!mbar_wait(L.empty(s), ph ^ 1, g, ERR_PRODUCER_EMPTY)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(L.full(s), STAGE_BYTES);
+          ptx::tma_load_2d(L.a(s), P::map_a(prm), L.full(s), kb * BK, a_row);
+          ptx::tma_load_2d(L.b(s), P::map_b(prm), L.full(s), kb * BK, n_blk * BN);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -194,27 +235,28 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         // both accumulators must have been drained by the epilogue of the previous tile
-        if (!mbar_wait(L.tmem_empty[0], acc_ph ^ 1, g, ERR_MMA_TMEM_EMPTY)) break;
-        if (!mbar_wait(L.tmem_empty[1], acc_ph ^ 1, g, ERR_MMA_TMEM_EMPTY)) break;
+        if (!mbar_wait(L.tmem_empty(0), acc_ph ^ 1, g, ERR_MMA_TMEM_EMPTY)) break;
+        if (!mbar_wait(L.tmem_empty(1), acc_ph ^ 1, g, ERR_MMA_TMEM_EMPTY)) break;
         ptx::tc_fence_after();
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(L.full[s], ph, g, ERR_MMA_FULL)) { ok = false; break; }
+          if (!mbar_wait(L.full(s), ph, g, ERR_MMA_FULL)) { ok = false; break; }
           ptx::tc_fence_after();
+          const uint32_t a0 = L.a(s), b0 = L.b(s);
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
 #pragma unroll
             for (int k = 0; k < BK_BYTES / UMMA_K_BYTES; ++k) {
-              uint64_t da = ptx::umma_desc_sw128(L.a[s] + half * (UMMA_M * BK_BYTES) + k * UMMA_K_BYTES);
-              uint64_t db = ptx::umma_desc_sw128(L.b[s] + k * UMMA_K_BYTES);
+              uint64_t da = ptx::umma_desc_sw128(a0 + half * (UMMA_M * BK_BYTES) + k * UMMA_K_BYTES);
+              uint64_t db = ptx::umma_desc_sw128(b0 + k * UMMA_K_BYTES);
               P::mma(tmem_base + half * UMMA_N, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             }
           }
-          ptx::umma_commit(L.empty[s]);       // stage reusable once these MMAs retire
+          ptx::umma_commit(L.empty(s));       // stage reusable once these MMAs retire
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        ptx::umma_commit(L.tmem_full[0]);
-        ptx::umma_commit(L.tmem_full[1]);
+        ptx::umma_commit(L.tmem_full(0));
+        ptx::umma_commit(L.tmem_full(1));
         acc_ph ^= 1;
       }
     }
@@ -227,8 +269,15 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(cp, tile, &m_blk, &n_blk);
-      if (!mbar_wait(L.tmem_full[half], acc_ph, g, ERR_EPI_TMEM_FULL)) { ok = false; break; }
+      P::tile_coords(prm, tile, &m_blk, &n_blk);
+      // the tensor core is busy with this tile: do useful work until the accumulator is ready
+      while (!ptx::mbar_try_wait(L.tmem_full(half), acc_ph)) {
+        if (!P::idle_work(prm, ew, lane, g)) {
+          if (!mbar_wait(L.tmem_full(half), acc_ph, g, ERR_EPI_TMEM_FULL)) ok = false;
+          break;
+        }
+      }
+      if (!ok) break;
       ptx::tc_fence_after();
       const int row0 = m_blk * BM + half * UMMA_M + quarter * 32;
 #pragma unroll 1
@@ -242,14 +291,15 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         if (lane == 0) ptx::tma_wait_group_read<0>();
         __syncwarp();
         // row = lane; 8 x 16-byte pieces, piece j lives at (j ^ (row & 7)) under the 128-byte swizzle
-        uint32_t rowbase = L.epi[ew] + lane * 128;
+        const uint32_t rowbase = L.epi(ew) + lane * 128;
+        const int col0 = n_blk * BN + c * EPI_COLS;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const uint32_t* src = &v[j >> 2][(j & 3) * 8];
-          uint32_t w0 = P::pack(src[0], src[1], prm, row0 + lane, n_blk * BN + c * EPI_COLS + j * 8);
-          uint32_t w1 = P::pack(src[2], src[3], prm, row0 + lane, n_blk * BN + c * EPI_COLS + j * 8 + 2);
-          uint32_t w2 = P::pack(src[4], src[5], prm, row0 + lane, n_blk * BN + c * EPI_COLS + j * 8 + 4);
-          uint32_t w3 = P::pack(src[6], src[7], prm, row0 + lane, n_blk * BN + c * EPI_COLS + j * 8 + 6);
+          uint32_t w0 = P::pack(src[0], src[1], prm, row0 + lane, col0 + j * 8);
+          uint32_t w1 = P::pack(src[2], src[3], prm, row0 + lane, col0 + j * 8 + 2);
+          uint32_t w2 = P::pack(src[4], src[5], prm, row0 + lane, col0 + j * 8 + 4);
+          uint32_t w3 = P::pack(src[6], src[7], prm, row0 + lane, col0 + j * 8 + 6);
           uint32_t dst = rowbase + ((j ^ (lane & 7)) << 4);
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
         }
@@ -257,18 +307,15 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         __syncwarp();
         if (lane == 0) {
           const CUtensorMap* map; int x, y;
-          P::out_target(prm, row0, n_blk * BN + c * EPI_COLS, &map, &x, &y);
-          if (map != nullptr) ptx::tma_store_2d(map, L.epi[ew], x, y);
+          P::out_target(prm, row0, col0, &map, &x, &y);
+          if (map != nullptr) ptx::tma_store_2d(map, L.epi(ew), x, y);
           ptx::tma_commit_group();
         }
       }
-      // all TMEM reads of this warp are done: hand the accumulator back
+      // all TMEM reads of this warp are done: hand the accumulator half back (4 warps share it)
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        // NUM_EPI_WARPS/2 warps share one accumulator half; each arrives once
-        ptx::mbar_arrive(L.tmem_empty[half]);
-      }
+      if (lane == 0) ptx::mbar_arrive(L.tmem_empty(half));
       if (P::kWaitStoresPerTile) {
         if (lane == 0) ptx::tma_wait_group<0>();
         __syncwarp();
@@ -277,12 +324,16 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       acc_ph ^= 1;
     }
     if (lane == 0) ptx::tma_wait_group<0>();
+    __syncwarp();
+    if (ok) P::epilogue_drain(prm, ew, lane, g);
   }
 
-  // ------------------------------ teardown ------------------------------------------
+  // ------------------------------ tail + teardown ---------------------------------------
   ptx::tc_fence_before();
   __syncthreads();
-  if (*L.abort_flag) {
+  if (!*L.abort_flag()) P::tail(prm, L, g);
+  __syncthreads();
+  if (*L.abort_flag()) {
     // let copies and MMAs that are still in flight land before smem/TMEM go away
     unsigned long long t0 = ptx::globaltimer();
     while (ptx::globaltimer() - t0 < 2000000ull) __nanosleep(1000);

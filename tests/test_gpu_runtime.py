@@ -112,8 +112,9 @@ def test_group_host_put_reaches_peer_heap(group):
     group.pes[0].put(xs[0], src, 2)          # PE 0 writes into PE 2's copy
     group.pes[0].quiet()
     assert torch.equal(xs[2], src) and int(xs[0].sum()) == 0 and int(xs[1].sum()) == 0
-    assert group.pes[3].atomic_fetch_add(xs[1], 9, 1) == 0
-    assert int(xs[1][0]) == 9
+    # a PE always names the target by its OWN symmetric address plus the target PE number
+    assert group.pes[3].atomic_fetch_add(xs[3], 9, 1) == 0
+    assert int(xs[1][0]) == 9 and int(xs[3][0]) == 0
 
 
 @pytest.mark.parametrize("dtype,n", [(torch.float32, 1000), (torch.float32, 300_000), (torch.bfloat16, 65_536),
