@@ -1,0 +1,161 @@
+"""Device collectives vs NCCL on identical buffers, teams of 2/4/8 PEs.
+
+    torchrun --nproc-per-node P -m roc_shmem_b200.bench.coll_bench [--max-bytes 1073741824] [--out file.json]
+
+Per-PE buffers 1 KiB .. max-bytes filled with N(0,1) (seed = PE); barrier, sum / max
+allreduce and reduce-scatter in fp32 and bf16, fcollect and alltoall.  Results are
+checked against NCCL's (bitwise for data movement; to rounding for reductions) and
+both are device-timed with CUDA events, max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+import roc_shmem_b200 as shmem
+
+
+def timed(fn, iters, rt):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    rt.barrier_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--out", default="")
+    ap.add_argument("--ctas", type=int, default=64)
+    ap.add_argument("--nvls", action="store_true")
+    args = ap.parse_args()
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    P = dist.get_world_size()
+    rt = shmem.init("device", device=local, heap_bytes=int(args.max_bytes * 2.5) + (256 << 20),
+                    nvls="on" if args.nvls else "off", coll_ctas=args.ctas)
+    me = rt.my_pe
+    dev = rt.device
+    rt.set_blocking(False)          # stream-ordered: calls enqueue kernels like NCCL does
+    rows = []
+    ok_all = True
+    torch.manual_seed(me)
+
+    # barrier latency
+    us = timed(lambda: rt.barrier_all(), 50, rt)
+    us_n = timed(lambda: dist.barrier(), 20, rt)
+    rows.append({"op": "barrier", "bytes": 0, "us": us, "nccl_us": us_n})
+
+    size = 1024
+    sizes = []
+    while size <= args.max_bytes:
+        sizes.append(size)
+        size *= 4
+    if sizes[-1] != args.max_bytes:
+        sizes.append(args.max_bytes)
+    src_all = rt.empty((args.max_bytes,), torch.uint8, align=1024)
+    dst_all = rt.empty((args.max_bytes,), torch.uint8, align=1024)
+    for dtype in (torch.float32, torch.bfloat16):
+        es = 2 if dtype == torch.bfloat16 else 4
+        for nbytes in sizes:
+            n = nbytes // es
+            n -= n % P
+            if n == 0:
+                continue
+            src = src_all[: n * es].view(dtype)
+            dst = dst_all[: n * es].view(dtype)
+            src.copy_(torch.randn(n, device=dev).to(dtype))
+            ref = src.clone()
+            iters = 20 if nbytes <= (16 << 20) else 5
+            for op, nccl_op in (("sum", dist.ReduceOp.SUM), ("max", dist.ReduceOp.MAX)):
+                rt.reduce(dst, src, op)
+                dist.all_reduce(ref, op=nccl_op)
+                torch.cuda.synchronize()
+                good = torch.allclose(dst.float(), ref.float(), rtol=2e-2 if es == 2 else 1e-5, atol=1e-2 if es == 2 else 1e-4)
+                ok_all &= bool(good)
+                ref.copy_(src)
+                us = timed(lambda: rt.reduce(dst, src, op), iters, rt)
+                us_n = timed(lambda: dist.all_reduce(ref, op=nccl_op), iters, rt)
+                ref.copy_(src)
+                busbw = 2 * (P - 1) / P * n * es / us / 1e3
+                rows.append({"op": f"allreduce_{op}", "dtype": str(dtype).split(".")[-1], "bytes": n * es, "us": us,
+                             "nccl_us": us_n, "busbw_GBps": busbw, "nccl_busbw_GBps": 2 * (P - 1) / P * n * es / us_n / 1e3,
+                             "ok": bool(good)})
+            # reduce-scatter (sum)
+            per = n // P
+            rs_dst = dst[:per]
+            rs_ref = torch.empty(per, device=dev, dtype=dtype)
+            rt.reduce_scatter(rs_dst, src, "sum")
+            dist.reduce_scatter_tensor(rs_ref, src)
+            torch.cuda.synchronize()
+            good = torch.allclose(rs_dst.float(), rs_ref.float(), rtol=2e-2 if es == 2 else 1e-5, atol=1e-2 if es == 2 else 1e-4)
+            ok_all &= bool(good)
+            us = timed(lambda: rt.reduce_scatter(rs_dst, src, "sum"), iters, rt)
+            us_n = timed(lambda: dist.reduce_scatter_tensor(rs_ref, src), iters, rt)
+            rows.append({"op": "reduce_scatter_sum", "dtype": str(dtype).split(".")[-1], "bytes": n * es, "us": us, "nccl_us": us_n,
+                         "busbw_GBps": (P - 1) / P * n * es / us / 1e3, "ok": bool(good)})
+    # data movement: fcollect and alltoall (bytes = per-PE total buffer)
+    for nbytes in sizes:
+        blk = nbytes // P
+        blk -= blk % 16
+        if blk == 0:
+            continue
+        src = src_all[:blk]
+        dst = dst_all[: blk * P]
+        src.copy_(torch.randint(0, 256, (blk,), device=dev, dtype=torch.uint8))
+        ref = torch.empty(blk * P, device=dev, dtype=torch.uint8)
+        iters = 20 if nbytes <= (16 << 20) else 5
+        rt.fcollect(dst, src)
+        dist.all_gather_into_tensor(ref, src)
+        torch.cuda.synchronize()
+        good = torch.equal(dst, ref)
+        ok_all &= bool(good)
+        us = timed(lambda: rt.fcollect(dst, src), iters, rt)
+        us_n = timed(lambda: dist.all_gather_into_tensor(ref, src), iters, rt)
+        rows.append({"op": "fcollect", "bytes": blk * P, "us": us, "nccl_us": us_n, "busbw_GBps": (P - 1) * blk / us / 1e3,
+                     "ok": bool(good)})
+        a_src = src_all[: blk * P]
+        a_src.copy_(torch.randint(0, 256, (blk * P,), device=dev, dtype=torch.uint8))
+        rt.alltoall(dst, a_src)
+        dist.all_to_all_single(ref, a_src)
+        torch.cuda.synchronize()
+        good = torch.equal(dst, ref)
+        ok_all &= bool(good)
+        us = timed(lambda: rt.alltoall(dst, a_src), iters, rt)
+        us_n = timed(lambda: dist.all_to_all_single(ref, a_src), iters, rt)
+        rows.append({"op": "alltoall", "bytes": blk * P, "us": us, "nccl_us": us_n, "busbw_GBps": (P - 1) * blk / us / 1e3,
+                     "ok": bool(good)})
+    rt.synchronize()
+    rt.set_blocking(True)
+    okt = torch.tensor([int(ok_all)], device=dev)
+    dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    if me == 0:
+        out = {"n_pes": P, "all_ok": bool(okt.item()), "rows": rows}
+        for r in rows:
+            print(json.dumps(r))
+        if args.out:
+            os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+            with open(args.out, "w") as f:
+                json.dump(out, f)
+    shmem.finalize()
+    dist.destroy_process_group()
+    if not bool(okt.item()):
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    main()

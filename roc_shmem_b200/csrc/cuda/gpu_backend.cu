@@ -273,7 +273,8 @@ class GpuBackend final : public Backend {
   }
 
   // ---- knobs used by the C entry points below ---------------------------------
-  void set_stream(cudaStream_t s) { stream_ = s ? s : own_stream_; }
+  // (cudaStream_t)-1 selects the runtime's own stream; any other handle (0 = the legacy default stream) is used as given.
+  void set_stream(cudaStream_t s) { stream_ = (s == reinterpret_cast<cudaStream_t>(-1)) ? own_stream_ : s; }
   cudaStream_t stream() const { return stream_; }
   void set_blocking(bool b) { blocking_ = b; }
   void set_coll_ctas(int n) { if (n >= 1 && n <= BSHMEM_MAX_COLL_CTAS) coll_ctas_ = n; }
@@ -330,6 +331,10 @@ class GpuBackend final : public Backend {
   }
   int fence() override { return BSHMEM_OK; }   // operations of one stream reach each PE in order
   int quiet() override {
+    // Stream mode: operations of the PE's stream complete in order, and whatever the caller
+    // enqueues next on that stream runs after them, so there is nothing to wait for on the
+    // host; bshmem_gpu_synchronize() is the explicit host-side wait.
+    if (!blocking_) return BSHMEM_OK;
     RT_TRY(cudaStreamSynchronize(stream_));
     return check_device_error("quiet");
   }
@@ -530,6 +535,19 @@ int bshmem_gpu_set_stream(bshmem_handle_t h, void* stream) {
   if (!g) return BSHMEM_ERR_STATE;
   g->set_stream(static_cast<cudaStream_t>(stream));
   return BSHMEM_OK;
+}
+int bshmem_gpu_get_stream(bshmem_handle_t h, void** stream) {
+  GpuBackend* g = gpu_of(h);
+  if (!g || !stream) return BSHMEM_ERR_STATE;
+  *stream = g->stream();
+  return BSHMEM_OK;
+}
+// Waits for everything enqueued on the PE's stream and reports device-side timeouts.
+int bshmem_gpu_synchronize(bshmem_handle_t h) {
+  GpuBackend* g = gpu_of(h);
+  if (!g) return BSHMEM_ERR_STATE;
+  if (cudaStreamSynchronize(g->stream()) != cudaSuccess) return BSHMEM_ERR_CUDA;
+  return g->check_device_error("synchronize");
 }
 int bshmem_gpu_set_blocking(bshmem_handle_t h, int blocking) {
   GpuBackend* g = gpu_of(h);

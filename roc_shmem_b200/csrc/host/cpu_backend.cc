@@ -288,7 +288,14 @@ class CpuBackend final : public Backend {
     return BSHMEM_OK;
   }
 
-  int sync(const CollGroup& g) override { return g.slot >= 0 ? sync_slot(g) : sync_psync(g); }
+  int sync(const CollGroup& g) override {
+    // a job that was aborted by global_exit does not run further collectives
+    if (w_->ctl()->aborted.load(std::memory_order_acquire)) {
+      record(BSHMEM_ERR_ABORTED, -1, BSHMEM_WHERE_BARRIER, 0, 0, 0);
+      return BSHMEM_ERR_ABORTED;
+    }
+    return g.slot >= 0 ? sync_slot(g) : sync_psync(g);
+  }
 
   int broadcast(const CollGroup& g, uint64_t dst_off, uint64_t src_off, uint64_t nbytes, int root) override {
     int rc = sync(g);   // the root's source is ready

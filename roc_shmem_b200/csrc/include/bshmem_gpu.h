@@ -45,7 +45,19 @@ uint64_t bshmem_gpu_heap_bytes(void* heap);
 
 int bshmem_gpu_init(void* heap, const bshmem_config_t* cfg, int coll_ctas, int own_heap, bshmem_handle_t* out);
 int bshmem_gpu_set_stream(bshmem_handle_t h, void* stream);
+int bshmem_gpu_get_stream(bshmem_handle_t h, void** stream);
+int bshmem_gpu_synchronize(bshmem_handle_t h);
 int bshmem_gpu_set_blocking(bshmem_handle_t h, int blocking);
+/* micro-benchmarks and device-API test kernels (p2p_kernels.cu); times in ns from %globaltimer */
+int bshmem_gpu_bench_pingpong(bshmem_handle_t h, void* flag_sym, int peer, int iters, int initiator, uint64_t* ns);
+int bshmem_gpu_bench_put_signal(bshmem_handle_t h, void* data_sym, void* sig_sym, uint64_t nbytes, int peer, int iters,
+                                int initiator, int threads, uint64_t* ns);
+int bshmem_gpu_bench_amo(bshmem_handle_t h, void* target_sym, int peer, int iters, int op, uint64_t* ns);
+int bshmem_gpu_bench_msgrate(bshmem_handle_t h, void* dest_sym, const void* src, uint64_t size, int peer, int windows,
+                             int ctas, int threads, uint64_t* ns);
+int bshmem_gpu_swarm_get(bshmem_handle_t h, void* local, const void* sym, uint64_t size, int peer, int ctas, int threads);
+int bshmem_gpu_api_selftest(bshmem_handle_t h, void* sym_i, void* sym_u, void* sym_f, int peer, int* results_dev);
+int bshmem_gpu_wg_collectives(bshmem_handle_t h, void* dst_sym, void* src_sym, int n, int* status_out);
 int bshmem_gpu_set_coll_ctas(bshmem_handle_t h, int n);
 int bshmem_gpu_set_nvls(bshmem_handle_t h, int on);
 int bshmem_gpu_get_state(bshmem_handle_t h, bshmem_dev_state_t* out);

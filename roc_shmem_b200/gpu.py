@@ -81,6 +81,15 @@ def cuda_lib() -> C.CDLL:
         f("bshmem_gpu_rma_kernel", _I, _VP, _VP, _VP, _U64, _I, _I, _I, _I, _I)
         f("bshmem_gpu_group_collective", _I, C.POINTER(_VP), _I, _I, _I, _I, _I, _I, _U64, _U64, _U64, _I)
         f("bshmem_gpu_group_team_split", _I, C.POINTER(_VP), _I, _I, _I, _I, _I, C.POINTER(_I))
+        f("bshmem_gpu_get_stream", _I, _VP, C.POINTER(_VP))
+        f("bshmem_gpu_synchronize", _I, _VP)
+        f("bshmem_gpu_bench_pingpong", _I, _VP, _VP, _I, _I, _I, C.POINTER(_U64))
+        f("bshmem_gpu_bench_put_signal", _I, _VP, _VP, _VP, _U64, _I, _I, _I, _I, C.POINTER(_U64))
+        f("bshmem_gpu_bench_amo", _I, _VP, _VP, _I, _I, _I, C.POINTER(_U64))
+        f("bshmem_gpu_bench_msgrate", _I, _VP, _VP, _VP, _U64, _I, _I, _I, _I, C.POINTER(_U64))
+        f("bshmem_gpu_swarm_get", _I, _VP, _VP, _VP, _U64, _I, _I, _I)
+        f("bshmem_gpu_api_selftest", _I, _VP, _VP, _VP, _VP, _I, _VP)
+        f("bshmem_gpu_wg_collectives", _I, _VP, _VP, _VP, _I, C.POINTER(_I))
         _declared = True
     return lib
 
@@ -124,11 +133,16 @@ class DeviceRuntime(Runtime):
 
     # stream-ordered mode: calls enqueue on `stream` and return; errors surface at quiet()
     def set_stream(self, stream: Optional[torch.cuda.Stream]) -> None:
-        s = C.c_void_p(stream.cuda_stream) if stream is not None else C.c_void_p(0)
+        # None -> the runtime's own stream; a torch stream (the default stream included) is used as given
+        s = C.c_void_p(stream.cuda_stream) if stream is not None else C.c_void_p(-1)
         self._check(self.lib.bshmem_gpu_set_stream(self.h, s))
 
     def set_blocking(self, blocking: bool) -> None:
         self._check(self.lib.bshmem_gpu_set_blocking(self.h, int(blocking)))
+
+    def synchronize(self) -> None:
+        """Host-side wait for everything enqueued on the PE's stream (stream mode's `quiet`)."""
+        self._check(self.lib.bshmem_gpu_synchronize(self.h))
 
     def set_coll_ctas(self, n: int) -> None:
         self._check(self.lib.bshmem_gpu_set_coll_ctas(self.h, n))
@@ -162,6 +176,52 @@ class DeviceRuntime(Runtime):
 
     def offset_of(self, t: torch.Tensor) -> int:
         return t.data_ptr() - int(self.lib.bshmem_heap_base(self.h))
+
+    # ---- device-API micro-benchmarks / functional kernels (csrc/cuda/p2p_kernels.cu) ----
+    def bench_pingpong(self, flag: torch.Tensor, peer: int, iters: int, initiator: bool) -> float:
+        """p + wait_until ping-pong with `peer`; returns one-way latency in microseconds."""
+        ns = C.c_uint64(0)
+        self._check(self.lib.bshmem_gpu_bench_pingpong(self.h, flag.data_ptr(), peer, iters, int(initiator), C.byref(ns)))
+        return ns.value / iters / 2 / 1e3
+
+    def bench_put_signal(self, data: torch.Tensor, sig: torch.Tensor, nbytes: int, peer: int, iters: int, initiator: bool,
+                         threads: int = 512) -> float:
+        ns = C.c_uint64(0)
+        self._check(self.lib.bshmem_gpu_bench_put_signal(self.h, data.data_ptr(), sig.data_ptr(), nbytes, peer, iters,
+                                                         int(initiator), threads, C.byref(ns)))
+        return ns.value / iters / 2 / 1e3
+
+    def bench_amo(self, target: torch.Tensor, peer: int, iters: int, op: int = D.AMO_FETCH_ADD) -> float:
+        ns = C.c_uint64(0)
+        self._check(self.lib.bshmem_gpu_bench_amo(self.h, target.data_ptr(), peer, iters, op, C.byref(ns)))
+        return ns.value / iters / 1e3
+
+    def bench_msgrate(self, dest: torch.Tensor, src: torch.Tensor, size: int, peer: int, windows: int, ctas: int,
+                      threads: int) -> float:
+        """put_nbi message rate (windows of 64 + quiet); returns million messages per second."""
+        ns = C.c_uint64(0)
+        self._check(self.lib.bshmem_gpu_bench_msgrate(self.h, dest.data_ptr(), src.data_ptr(), size, peer, windows, ctas,
+                                                      threads, C.byref(ns)))
+        return ctas * threads * 64 * windows / (ns.value * 1e-9) / 1e6
+
+    def swarm_get(self, local: torch.Tensor, sym: torch.Tensor, size: int, peer: int, ctas: int, threads: int) -> None:
+        self._check(self.lib.bshmem_gpu_swarm_get(self.h, local.data_ptr(), sym.data_ptr(), size, peer, ctas, threads))
+
+    def api_selftest(self, peer: int) -> list[int]:
+        """Runs the typed device API (p/g, all atomics, ptr, test) against `peer` inside one kernel."""
+        si = self.zeros((4,), torch.int32)
+        su = self.zeros((4,), torch.int64)
+        sf = self.zeros((4,), torch.float32)
+        res = torch.full((64,), -2, dtype=torch.int32, device=self.device)
+        self._check(self.lib.bshmem_gpu_api_selftest(self.h, si.data_ptr(), su.data_ptr(), sf.data_ptr(), peer, res.data_ptr()))
+        out = res.tolist()
+        self.barrier_all()
+        return out[:out.index(-1)]
+
+    def wg_collectives(self, dst: torch.Tensor, src: torch.Tensor) -> int:
+        st = C.c_int(-1)
+        self._check(self.lib.bshmem_gpu_wg_collectives(self.h, dst.data_ptr(), src.data_ptr(), src.numel(), C.byref(st)))
+        return st.value
 
 
 def init_device_runtime(boot: Bootstrap, cfg: Config, device: Optional[int] = None, proxy: bool = False) -> DeviceRuntime:
@@ -232,6 +292,8 @@ def init_device_runtime(boot: Bootstrap, cfg: Config, device: Optional[int] = No
     rt.bootstrap = boot
     rt.heap_mode = "vmm" if mode == 0 else "ipc"
     rt.nvls = nvls_on
+    # Order the runtime's operations with the caller's PyTorch work: same stream as torch ops.
+    rt.set_stream(torch.cuda.current_stream())
     if nvls_on:
         rt.set_nvls(True)
     if n > 1:
@@ -266,6 +328,7 @@ class LocalGroup:
             _gpu_error(self.lib, "gpu_init", self.lib.bshmem_gpu_init(self.heaps[pe], C.byref(nc), cfg.coll_ctas, 1, C.byref(h)))
             rt = DeviceRuntime(self.lib, h.value, torch.device("cuda", device), self.heaps[pe])
             rt.config = cfg
+            rt.set_stream(torch.cuda.current_stream())
             self.pes.append(rt)
         self._handles = (C.c_void_p * n_pes)(*[rt.h.value for rt in self.pes])
 

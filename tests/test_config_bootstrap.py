@@ -1,0 +1,61 @@
+"""Config/env handling and the store bootstrap (rank/size, all-gather, barrier, fd passing)."""
+import multiprocessing as mp
+import os
+import tempfile
+
+import pytest
+import torch.distributed as dist
+
+from roc_shmem_b200.bootstrap import Bootstrap
+from roc_shmem_b200.config import Config
+
+
+def test_config_defaults_env_aliases_and_overrides(monkeypatch):
+    c = Config.from_env()
+    assert c.heap_bytes == 1 << 30 and c.max_teams == 40 and c.backend == "auto" and c.nvls == "off"
+    monkeypatch.setenv("ROC_SHMEM_HEAP_SIZE", "64M")           # the reference's spelling is accepted
+    monkeypatch.setenv("B200SHMEM_MAX_NUM_TEAMS", "8")
+    monkeypatch.setenv("B200SHMEM_DEBUG", "1")
+    c = Config.from_env(timeout_ms=5)
+    assert c.heap_bytes == 64 << 20 and c.max_teams == 8 and c.debug is True and c.timeout_ms == 5
+    monkeypatch.setenv("B200SHMEM_HEAP_SIZE", "2GiB")          # the native spelling wins over the alias
+    assert Config.from_env().heap_bytes == 2 << 30
+    with pytest.raises(ValueError):
+        Config.from_env(backend="mpi")
+    with pytest.raises(ValueError):
+        Config.from_env(proxy_slots=100)
+    with pytest.raises(TypeError):
+        Config.from_env(no_such_field=1)
+
+
+def _boot_worker(rank, world, path, q):
+    store = dist.FileStore(path, world)
+    b = Bootstrap(store, rank, world, timeout_s=30)
+    got = b.allgather({"rank": rank, "blob": bytes([rank]) * 3})
+    b.barrier()
+    root = b.broadcast("hello" if rank == 1 else None, root=1)
+    r, w = os.pipe()
+    os.write(w, f"from-{rank}".encode() * (world - 1))       # one 6-byte message per reader of this pipe
+    fds = b.exchange_fds([r])
+    texts = [os.read(fds[p][0], 6).decode() if p != rank else f"from-{rank}" for p in range(world)]
+    q.put((rank, [g["rank"] for g in got], root, texts))
+
+
+def test_bootstrap_allgather_barrier_broadcast_and_fd_exchange():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "store")
+        procs = [ctx.Process(target=_boot_worker, args=(r, 3, path, q)) for r in range(3)]
+        [p.start() for p in procs]
+        res = sorted(q.get(timeout=120) for _ in range(3))
+        [p.join(30) for p in procs]
+    for rank, ranks, root, texts in res:
+        assert ranks == [0, 1, 2] and root == "hello"
+        assert texts == ["from-0", "from-1", "from-2"]        # each descriptor really is the peer's pipe
+
+
+def test_bootstrap_barrier_times_out_when_a_rank_never_joins():
+    b = Bootstrap(dist.HashStore(), 0, 2, timeout_s=0.3)
+    with pytest.raises(TimeoutError):
+        b.barrier()
