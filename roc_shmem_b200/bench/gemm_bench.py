@@ -45,11 +45,12 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--mid", action="store_true", help="one launch of a 4-wave problem (592 tiles) for profiler captures")
     ap.add_argument("--max-ctas", type=int, default=0)
     args = ap.parse_args()
     dev = torch.device("cuda")
-    if args.small:
-        M, N, K = 2048, 2048, 2048
+    if args.small or args.mid:
+        M, N, K = (4096, 9472, 4096) if args.mid else (2048, 2048, 2048)
         a = torch.randn(M, K, device=dev).to(torch.bfloat16)
         b = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
         pad = torch.empty(160 << 20, dtype=torch.uint8, device=dev)

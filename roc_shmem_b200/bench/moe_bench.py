@@ -1,0 +1,139 @@
+"""MoE expert-parallel layer: device-API dispatch/combine + grouped tcgen05 GEMMs versus
+NCCL all_to_all + cuBLAS, forward + backward, device-timed (max over ranks).
+
+    torchrun --nproc-per-node P -m roc_shmem_b200.bench.moe_bench [--small] [--iters 5] [--out file.json]
+
+Config: Mixtral-style, 8 experts, top-2, hidden 4096, expert ffn 14336 (SwiGLU), 16384 tokens per
+rank, bf16; router logits from N(0,1) activations and weights, expert weights N(0,0.02).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+import roc_shmem_b200 as shmem
+from roc_shmem_b200.baseline.moe import NcclMoE
+from roc_shmem_b200.ops.moe import MoELayer, interleave_gate_up
+
+
+def timed(fn, iters, rt):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    rt.barrier_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    if dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--out", default="")
+    ap.add_argument("--no-baseline", action="store_true")
+    args = ap.parse_args()
+    rank, P = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    E, topk = 8, 2
+    if args.small:
+        T, H, F = 1024, 512, 1024
+    else:
+        T, H, F = args.tokens, 4096, 14336
+    G = E // P
+    cap_rows = int(T * topk * P / E * 1.25)
+    heap = (G * cap_rows * H * 2) + 2 * (T * topk * H * 2) + (512 << 20)
+    rt = shmem.init("device", device=local, heap_bytes=heap, timeout_ms=20000)
+    dev = rt.device
+    torch.manual_seed(7)                                   # same weights on every rank, sliced per rank
+    wr = torch.randn(E, H, device=dev).to(torch.bfloat16)
+    w1 = (torch.randn(E, F, H, device=dev) * 0.02).to(torch.bfloat16)[rank * G:(rank + 1) * G].contiguous()
+    w3 = (torch.randn(E, F, H, device=dev) * 0.02).to(torch.bfloat16)[rank * G:(rank + 1) * G].contiguous()
+    w2 = (torch.randn(E, H, F, device=dev) * 0.02).to(torch.bfloat16)[rank * G:(rank + 1) * G].contiguous()
+    torch.manual_seed(100 + rank)
+    x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    dout = torch.randn(T, H, device=dev).to(torch.bfloat16)
+
+    layer = MoELayer(rt, H, F, E, topk, T, capacity_factor=1.25, training=True, timeout_ms=20000)
+    layer.wr.copy_(wr)
+    layer.w2.copy_(w2)
+    for g in range(G):
+        layer.w13[g].copy_(interleave_gate_up(w1[g], w3[g]))
+    layer.sync_transposes()
+    rt.set_blocking(False)                                 # stream-ordered like the NCCL baseline
+
+    res = {"world": P, "tokens_per_rank": T, "hidden": H, "ffn": F, "experts": E, "topk": topk, "capacity_rows": layer.cap}
+    y = layer.forward(x).clone()
+    dx = layer.backward(dout).clone()
+    torch.cuda.synchronize()
+    layer.check()
+
+    ok = True
+    if not args.no_baseline:
+        base = NcclMoE(wr, w1.clone(), w3.clone(), w2.clone(), topk)
+        xb = x.clone().requires_grad_(True)
+        yb = base(xb)
+        yb.backward(dout)
+        torch.cuda.synchronize()
+        sy, sdx = yb.detach().float().abs().max().item(), xb.grad.float().abs().max().item()
+        ey = (y.float() - yb.detach().float()).abs().max().item()
+        edx = (dx.float() - xb.grad.float()).abs().max().item()
+        ew2 = (layer.dw2.float() - base.w2.grad.float()).abs().max().item() / (base.w2.grad.float().abs().max().item() + 1e-9)
+        ok = ey <= 5e-2 * sy + 2e-2 and edx <= 8e-2 * sdx + 2e-2 and ew2 <= 8e-2
+        res.update({"fwd_max_abs_diff": ey, "fwd_scale": sy, "dx_max_abs_diff": edx, "dx_scale": sdx, "dw2_rel_diff": ew2})
+
+    def ours():
+        layer.forward(x)
+        layer.backward(dout)
+
+    ms = timed(ours, args.iters, rt)
+    layer.check()
+    ms_f = timed(lambda: layer.forward(x), args.iters, rt)
+    res.update({"ms_fwd_bwd": ms, "ms_fwd": ms_f})
+    # useful FLOPs: 3 GEMM pairs forward (gate, up, down), twice that backward
+    rows = float(layer.recv_count.sum().item())
+    flops_fwd = 2.0 * rows * H * F * 3
+    res["tflops_fwd_bwd_per_gpu"] = 3 * flops_fwd / (ms * 1e-3) / 1e12
+    if not args.no_baseline:
+        def theirs():
+            xb2 = x.clone().requires_grad_(True)
+            base.zero_grad(set_to_none=True)
+            base(xb2).backward(dout)
+        ms_b = timed(theirs, max(2, args.iters // 2), rt)
+        with torch.no_grad():
+            ms_bf = timed(lambda: base(x), max(2, args.iters // 2), rt)
+        res.update({"ms_fwd_bwd_nccl_cublas": ms_b, "ms_fwd_nccl_cublas": ms_bf, "speedup_fwd_bwd": ms_b / ms, "speedup_fwd": ms_bf / ms_f})
+    okt = torch.tensor([int(ok)], device=dev)
+    dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    res["all_ranks_ok"] = bool(okt.item())
+    rt.synchronize()
+    rt.set_blocking(True)
+    if rank == 0:
+        line = json.dumps(res)
+        print(line, flush=True)
+        if args.out:
+            os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+            with open(args.out, "w") as f:
+                f.write(line + "\n")
+    shmem.finalize()
+    dist.destroy_process_group()
+    if not res["all_ranks_ok"]:
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    main()

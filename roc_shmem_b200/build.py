@@ -44,7 +44,7 @@ CUDA_TARGETS = {
     "libbshmem_cuda.so": (["cuda/vmm_heap.cu", "cuda/gpu_backend.cu", "cuda/p2p_kernels.cu"] + HOST_SOURCES, []),
     "libbshmem_gemm.so": (["cuda/gemm_bf16.cu"], []),
     "libbshmem_fused.so": (["cuda/fused_tp.cu"], []),
-    "libbshmem_moe.so": (["cuda/moe_kernels.cu"], []),
+    "libbshmem_moe.so": (["cuda/moe_kernels.cu", "cuda/moe_gemm.cu"], []),
     "libbshmem_fp8.so": (["cuda/gemm_fp8.cu"], []),
 }
 

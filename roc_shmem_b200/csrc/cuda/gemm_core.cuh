@@ -155,7 +155,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Defaults a policy can inherit.
 struct PolicyDefaults {
   static constexpr bool kWaitStoresPerTile = false;
+  // Gated epilogue: inside every 64-column chunk, columns 0-31 are gate pre-activations and 32-63 the
+  // matching up-projections; the epilogue writes silu(gate) * up, i.e. half as many output columns.
+  static constexpr bool kGated = false;
+  template <class Params> __device__ static __forceinline__ int b_row(const Params&, int, int n_blk) { return n_blk * BN; }
   template <class Params> __device__ static __forceinline__ bool a_ready(const Params&, int, Guard&) { return true; }
+  // k-blocks of the tile's reduction (ragged per group in the grouped weight-gradient GEMM)
+  template <class Params> __device__ static __forceinline__ int num_kb(const Params& p, int, int bk) {
+    return (p.core.K + bk - 1) / bk;
+  }
+  template <class Params> __device__ static __forceinline__ int num_tiles(const Params& p) {
+    return p.core.num_m_blocks * p.core.num_n_blocks;
+  }
   template <class Params> __device__ static __forceinline__ void tile_done(const Params&, int, int, int, int) {}
   // work for an epilogue warp while the tensor core is busy; false = nothing to do
   template <class Params> __device__ static __forceinline__ bool idle_work(const Params&, int, int, Guard&) { return false; }
@@ -183,9 +194,8 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
   const Smem L = carve_smem(smem_raw);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = cp.num_m_blocks * cp.num_n_blocks;
+  const int num_tiles = P::num_tiles(prm);
   constexpr int BK = BK_BYTES / P::kElemBytes;   // k-block in elements
-  const int num_kb = (cp.K + BK - 1) / BK;
   Guard g{cp.err, L.abort_flag(), cp.timeout_ns};
 
   if (threadIdx.x == 0) {
@@ -217,11 +227,13 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         P::tile_coords(prm, tile, &m_blk, &n_blk);
         if (!P::a_ready(prm, m_blk, g)) break;
         const int a_row = P::a_row(prm, m_blk);
+        const int b_row = P::b_row(prm, m_blk, n_blk);
+        const int num_kb = P::num_kb(prm, m_blk, BK);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(L.empty(s), ph ^ 1, g, ERR_PRODUCER_EMPTY)) { ok = false; break; }
           ptx::mbar_arrive_expect_tx(L.full(s), STAGE_BYTES);
           ptx::tma_load_2d(L.a(s), P::map_a(prm), L.full(s), kb * BK, a_row);
-          ptx::tma_load_2d(L.b(s), P::map_b(prm), L.full(s), kb * BK, n_blk * BN);
+          ptx::tma_load_2d(L.b(s), P::map_b(prm), L.full(s), kb * BK, b_row);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -238,6 +250,9 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         if (!mbar_wait(L.tmem_empty(0), acc_ph ^ 1, g, ERR_MMA_TMEM_EMPTY)) break;
         if (!mbar_wait(L.tmem_empty(1), acc_ph ^ 1, g, ERR_MMA_TMEM_EMPTY)) break;
         ptx::tc_fence_after();
+        int m_blk, n_blk;
+        P::tile_coords(prm, tile, &m_blk, &n_blk);
+        const int num_kb = P::num_kb(prm, m_blk, BK);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(L.full(s), ph, g, ERR_MMA_FULL)) { ok = false; break; }
           ptx::tc_fence_after();
@@ -280,36 +295,76 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       if (!ok) break;
       ptx::tc_fence_after();
       const int row0 = m_blk * BM + half * UMMA_M + quarter * 32;
+      if constexpr (!P::kGated) {
 #pragma unroll 1
-      for (int c = 0; c < BN / EPI_COLS; ++c) {
-        uint32_t v[2][32];
-        uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * UMMA_N + c * EPI_COLS;
-        ptx::tmem_ld_32x32b_x32(taddr, v[0]);
-        ptx::tmem_ld_32x32b_x32(taddr + 32, v[1]);
-        ptx::tmem_ld_wait();
-        // the previous chunk's TMA store must have finished reading the staging buffer
-        if (lane == 0) ptx::tma_wait_group_read<0>();
-        __syncwarp();
-        // row = lane; 8 x 16-byte pieces, piece j lives at (j ^ (row & 7)) under the 128-byte swizzle
-        const uint32_t rowbase = L.epi(ew) + lane * 128;
-        const int col0 = n_blk * BN + c * EPI_COLS;
+        for (int c = 0; c < BN / EPI_COLS; ++c) {
+          uint32_t v[2][32];
+          uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * UMMA_N + c * EPI_COLS;
+          ptx::tmem_ld_32x32b_x32(taddr, v[0]);
+          ptx::tmem_ld_32x32b_x32(taddr + 32, v[1]);
+          ptx::tmem_ld_wait();
+          // the previous chunk's TMA store must have finished reading the staging buffer
+          if (lane == 0) ptx::tma_wait_group_read<0>();
+          __syncwarp();
+          // row = lane; 8 x 16-byte pieces, piece j lives at (j ^ (row & 7)) under the 128-byte swizzle
+          const uint32_t rowbase = L.epi(ew) + lane * 128;
+          const int col0 = n_blk * BN + c * EPI_COLS;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t* src = &v[j >> 2][(j & 3) * 8];
-          uint32_t w0 = P::pack(src[0], src[1], prm, row0 + lane, col0 + j * 8);
-          uint32_t w1 = P::pack(src[2], src[3], prm, row0 + lane, col0 + j * 8 + 2);
-          uint32_t w2 = P::pack(src[4], src[5], prm, row0 + lane, col0 + j * 8 + 4);
-          uint32_t w3 = P::pack(src[6], src[7], prm, row0 + lane, col0 + j * 8 + 6);
-          uint32_t dst = rowbase + ((j ^ (lane & 7)) << 4);
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t* src = &v[j >> 2][(j & 3) * 8];
+            uint32_t w0 = P::pack(src[0], src[1], prm, row0 + lane, col0 + j * 8);
+            uint32_t w1 = P::pack(src[2], src[3], prm, row0 + lane, col0 + j * 8 + 2);
+            uint32_t w2 = P::pack(src[4], src[5], prm, row0 + lane, col0 + j * 8 + 4);
+            uint32_t w3 = P::pack(src[6], src[7], prm, row0 + lane, col0 + j * 8 + 6);
+            uint32_t dst = rowbase + ((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const CUtensorMap* map; int x, y;
+            P::out_target(prm, row0, col0, &map, &x, &y);
+            if (map != nullptr) ptx::tma_store_2d(map, L.epi(ew), x, y);
+            ptx::tma_commit_group();
+          }
         }
-        ptx::fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const CUtensorMap* map; int x, y;
-          P::out_target(prm, row0, col0, &map, &x, &y);
-          if (map != nullptr) ptx::tma_store_2d(map, L.epi(ew), x, y);
-          ptx::tma_commit_group();
+      } else {
+        // two 64-column chunks (32 gate + 32 up each) make one 64-column output chunk
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / (2 * EPI_COLS); ++c2) {
+          if (lane == 0) ptx::tma_wait_group_read<0>();
+          __syncwarp();
+          const uint32_t rowbase = L.epi(ew) + lane * 128;
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            uint32_t v[2][32];
+            uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * UMMA_N + (2 * c2 + hc) * EPI_COLS;
+            ptx::tmem_ld_32x32b_x32(taddr, v[0]);        // gate
+            ptx::tmem_ld_32x32b_x32(taddr + 32, v[1]);   // up
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t w[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float g0 = __uint_as_float(v[0][j * 8 + 2 * q]), g1 = __uint_as_float(v[0][j * 8 + 2 * q + 1]);
+                float u0 = __uint_as_float(v[1][j * 8 + 2 * q]), u1 = __uint_as_float(v[1][j * 8 + 2 * q + 1]);
+                float h0 = g0 / (1.f + __expf(-g0)) * u0, h1 = g1 / (1.f + __expf(-g1)) * u1;
+                w[q] = pack_bf16(h0, h1);
+              }
+              uint32_t dst = rowbase + (((hc * 4 + j) ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const CUtensorMap* map; int x, y;
+            // output column index is half the accumulator column index
+            P::out_target(prm, row0, (n_blk * BN + c2 * 2 * EPI_COLS) / 2, &map, &x, &y);
+            if (map != nullptr) ptx::tma_store_2d(map, L.epi(ew), x, y);
+            ptx::tma_commit_group();
+          }
         }
       }
       // all TMEM reads of this warp are done: hand the accumulator half back (4 warps share it)

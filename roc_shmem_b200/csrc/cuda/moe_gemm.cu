@@ -1,0 +1,181 @@
+// moe_gemm.cu — grouped (per-expert) tcgen05 GEMM for the MoE layer, built on the
+// persistent main loop of gemm_core.cuh.
+//
+//   C_g = A_g · B_g^T  for every local expert g, all operands K-major bf16:
+//     rows mode   A: [G][cap rows][K]   B: [G][N][K]    C: [G][cap][N]
+//                 the row count of group g is read from device memory (tokens that arrived),
+//                 so no host synchronisation is needed between dispatch and the GEMM;
+//     ragged-K    A: [G][M][cap]        B: [G][N][cap]  C: [G][M][N]
+//                 the reduction length of group g is the device-side token count (weight
+//                 gradients over transposed, zero-padded activations).
+//   Optional gated epilogue (SwiGLU fused: interleaved gate/up columns → silu(g)·u) and an
+//   optional wait on the dispatch arrival words before the first A load.
+// There is no grouped GEMM in the reference; the layout conventions are those of
+// moe_kernels.cu.
+#include "gemm_core.cuh"
+#include "moe_common.h"
+#include "tma_host.h"
+
+using namespace bshmem;
+using namespace bshmem::gemm;
+
+namespace {
+
+struct GroupedParams {
+  CoreParams core;                 // N = output columns of the accumulator, K = full reduction length
+  CUtensorMap map_a, map_b, map_c;
+  const int* rows;                 // [G] valid rows per group (rows mode) or null (all `fixed_rows`)
+  const int* klen;                 // [G] reduction length per group (ragged-K mode) or null
+  int G, fixed_rows;
+  int a_blocks_per_group;          // 256-row blocks between consecutive groups in A and C
+  int b_rows_per_group;            // rows between consecutive groups in B
+  int group_m;
+  int P;                           // arrival wait: number of words, 0 = no wait
+  const unsigned long long* arrive;
+  const int* expected;
+};
+
+template <bool kGatedEpi>
+struct Grouped : PolicyDefaults {
+  using Params = GroupedParams;
+  static constexpr int kElemBytes = 2;
+  static constexpr uint32_t kIdesc = ptx::umma_idesc(1, 1, UMMA_M, UMMA_N);
+  static constexpr bool kGated = kGatedEpi;
+  __device__ static __forceinline__ const CoreParams& core(const Params& p) { return p.core; }
+  __device__ static __forceinline__ const CUtensorMap* map_a(const Params& p) { return &p.map_a; }
+  __device__ static __forceinline__ const CUtensorMap* map_b(const Params& p) { return &p.map_b; }
+  __device__ static __forceinline__ int group_rows(const Params& p, int g) { return p.rows ? p.rows[g] : p.fixed_rows; }
+  __device__ static __forceinline__ int num_tiles(const Params& p) {
+    int t = 0;
+    for (int g = 0; g < p.G; ++g) t += ((group_rows(p, g) + BM - 1) / BM) * p.core.num_n_blocks;
+    return t;
+  }
+  // m_blk is a virtual block index: group * a_blocks_per_group + block inside the group
+  __device__ static __forceinline__ void tile_coords(const Params& p, int tile, int* m_blk, int* n_blk) {
+    int g = 0, mb_g = 0;
+    for (; g < p.G; ++g) {
+      mb_g = (group_rows(p, g) + BM - 1) / BM;
+      int tg = mb_g * p.core.num_n_blocks;
+      if (tile < tg) break;
+      tile -= tg;
+    }
+    int per = p.group_m * p.core.num_n_blocks;
+    int sg = tile / per, first = sg * p.group_m;
+    int rows = min(p.group_m, mb_g - first);
+    int in = tile - sg * per;
+    *m_blk = g * p.a_blocks_per_group + first + in % rows;
+    *n_blk = in / rows;
+  }
+  __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * BM; }
+  __device__ static __forceinline__ int b_row(const Params& p, int m_blk, int n_blk) {
+    return (m_blk / p.a_blocks_per_group) * p.b_rows_per_group + n_blk * BN;
+  }
+  __device__ static __forceinline__ int num_kb(const Params& p, int m_blk, int bk) {
+    int k = p.klen ? p.klen[m_blk / p.a_blocks_per_group] : p.core.K;
+    int n = (k + bk - 1) / bk;
+    return n < 1 ? 1 : n;     // an empty group still runs one (all-zero) k-block so that C becomes 0
+  }
+  __device__ static __forceinline__ bool a_ready(const Params& p, int, Guard& g) {
+    for (int s = 0; s < p.P; ++s)
+      if (!wait_ge<true>(p.arrive + s, (unsigned long long)p.expected[s], g, ERR_PEER_SIGNAL)) return false;
+    if (p.P) ptx::fence_proxy_async_all();   // peer stores (generic proxy) before the TMA reads
+    return true;
+  }
+  __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    ptx::umma_f16(d, a, b, idesc, acc);
+  }
+  __device__ static __forceinline__ uint32_t pack(uint32_t lo, uint32_t hi, const Params&, int, int) {
+    return pack_bf16(__uint_as_float(lo), __uint_as_float(hi));
+  }
+  __device__ static __forceinline__ void out_target(const Params& p, int row, int col, const CUtensorMap** map, int* x, int* y) {
+    *map = &p.map_c;       // rows beyond a group's count are scratch inside the group's own region
+    *x = col;
+    *y = row;
+  }
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1) grouped_gemm_kernel(const __grid_constant__ GroupedParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_mainloop<Grouped<false>>(prm, smem_raw);
+}
+__global__ void __launch_bounds__(NUM_THREADS, 1) grouped_gemm_gated_kernel(const __grid_constant__ GroupedParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_mainloop<Grouped<true>>(prm, smem_raw);
+}
+
+int* g_err_dev[64] = {};
+int g_sms[64] = {};
+
+int ensure(int dev) {
+  if (g_err_dev[dev]) return 0;
+  BSHMEM_CUDA_TRY(cudaMalloc(&g_err_dev[dev], sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaMemset(g_err_dev[dev], 0, sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_gated_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* bshmem_moe_gemm_last_error() { return host::last_error().c_str(); }
+
+// Grouped GEMM.  A: [G * a_rows_per_group, K] (lda), B: [G * b_rows_per_group, K] (ldb), C: [G * a_rows_per_group, N_out] (ldc).
+//   rows_dev   per-group valid row counts on the device, or null → every group has `fixed_rows` rows
+//   klen_dev   per-group reduction lengths on the device, or null → K
+//   gated      1: accumulator columns are interleaved gate/up, C gets N/2 columns of silu(gate)*up
+//   arrive/expected/P  optional arrival words to wait for before the first load (P = 0: none)
+int bshmem_moe_grouped_gemm(const void* A, const void* B, void* C, int G, int a_rows_per_group, int b_rows_per_group, int N, int K,
+                            int lda, int ldb, int ldc, const int* rows_dev, int fixed_rows, const int* klen_dev, int gated,
+                            const void* arrive, const int* expected, int P, void* stream, int timeout_ms, int max_ctas) {
+  if (G < 1 || a_rows_per_group % BM || N % BN || K % 8 || lda % 8 || ldb % 8 || ldc % 8) {
+    host::last_error() = "grouped gemm: needs rows-per-group % 256 == 0, N % 256 == 0, K and leading dimensions % 8 == 0";
+    return 1;
+  }
+  int dev = 0;
+  BSHMEM_CUDA_TRY(cudaGetDevice(&dev));
+  int rc = ensure(dev);
+  if (rc) return rc;
+  GroupedParams p;
+  memset(&p, 0, sizeof(p));
+  p.core.M = G * a_rows_per_group; p.core.N = N; p.core.K = K;
+  p.core.num_m_blocks = p.core.M / BM; p.core.num_n_blocks = N / BN;
+  p.core.group_m = 16;
+  p.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 4000) * 1000000ull;
+  p.core.err = g_err_dev[dev];
+  p.rows = rows_dev; p.klen = klen_dev; p.G = G; p.fixed_rows = fixed_rows > 0 ? fixed_rows : a_rows_per_group;
+  p.a_blocks_per_group = a_rows_per_group / BM;
+  p.b_rows_per_group = b_rows_per_group;
+  p.group_m = 16;
+  p.P = P; p.arrive = static_cast<const unsigned long long*>(arrive); p.expected = expected;
+  rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)G * a_rows_per_group, K, lda, BM, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, (uint64_t)G * b_rows_per_group, K, ldb, BN, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&p.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, (uint64_t)G * a_rows_per_group, gated ? N / 2 : N, ldc, 32, EPI_COLS);
+  if (rc) return rc;
+  int ctas = g_sms[dev];
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (gated) grouped_gemm_gated_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  else grouped_gemm_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int bshmem_moe_gemm_error_site(int clear) {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || !g_err_dev[dev]) return 0;
+  cudaMemcpy(&v, g_err_dev[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (clear && v) cudaMemset(g_err_dev[dev], 0, sizeof(int));
+  return v;
+}
+
+int* bshmem_moe_gemm_error_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || ensure(dev)) return nullptr;
+  return g_err_dev[dev];
+}
+
+}  // extern "C"
