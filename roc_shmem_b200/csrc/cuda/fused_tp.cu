@@ -21,6 +21,7 @@
 // back-to-back calls need no extra barrier.  No counterpart in the reference (it has
 // neither GEMMs nor fused collectives); the signalling follows its put + flag idiom
 // (library/src/gpu_ib/context_ib_tmpl_device.hpp:184-236).
+#include <cstdlib>
 #include <vector>
 
 #include "../include/bshmem_device.cuh"
@@ -48,6 +49,9 @@ struct RsParams {
   const __nv_bfloat16* staging_local;           // [P][rows_per_owner][N] (this call's parity)
   __nv_bfloat16* out;                           // [rows_per_owner, N]
   long long ldo;
+  unsigned int* ticket;                         // local [2]: reduction work counter of this call's parity
+  unsigned long long call;
+  int tune;                                     // bit 0: no reduction during the GEMM, bit 1: skip the reduction (timing experiments only)
 };
 
 struct GemmRs : PolicyDefaults {
@@ -92,48 +96,134 @@ struct GemmRs : PolicyDefaults {
       ptx::red_release_sys_add_u64(reinterpret_cast<uint64_t*>(p.sig_remote[owner] + idx), 1);
     }
   }
-  // Reduce the partials of the tiles this PE owns: 64-row slices of 256 columns, round-robin over CTAs,
-  // earliest sub-round first.
-  __device__ static __forceinline__ void tail(const Params& p, const Smem& L, Guard& g) {
-    const int num_n = p.core.num_n_blocks;
-    const int ntasks = p.blocks_per_owner * num_n * 4;
+  // ---- reduction of the partials this PE owns --------------------------------------------------
+  // Work unit: 8 rows x 256 columns of one owned tile (32 units per tile), handed out by a ticket
+  // counter in tile order, which is also the order in which the tiles' partials arrive.
+  static constexpr int kUnitsPerTile = BM / 8;
+  // PP = number of partials (compile time), R = rows whose loads are issued together (PP * R loads in flight)
+  template <int PP, int R>
+  __device__ static __forceinline__ void reduce_rows(const Params& p, int r0, long long c) {
     const long long N = p.core.N;
-    for (int task = blockIdx.x; task < ntasks; task += gridDim.x) {
-      int tile = task >> 2, slice = task & 3;
-      int blk = tile / num_n, n_blk = tile - blk * num_n;
-      if (threadIdx.x == 0)
-        *L.scratch() = wait_ge<true>(p.sig_local + tile, p.expect, g, ERR_PEER_SIGNAL) ? 1 : 0;
-      __syncthreads();
-      const bool ok = *L.scratch() != 0;
-      if (ok) {
-        const int r0 = blk * BM + slice * 64;
-        for (int v = threadIdx.x; v < 64 * (BN / 8); v += blockDim.x) {
-          int r = r0 + v / (BN / 8);
-          long long c = (long long)n_blk * BN + (v % (BN / 8)) * 8;
+#pragma unroll 1
+    for (int j = 0; j < 8; j += R) {
+      uint4 x[R][PP];
+#pragma unroll
+      for (int q = 0; q < R; ++q)
+#pragma unroll
+        for (int s = 0; s < PP; ++s)
+          x[q][s] = ptx::ld_relaxed_v4(p.staging_local + ((long long)s * p.rows_per_owner + r0 + j + q) * N + c);
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int s = 0; s < PP; ++s) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x[q][s]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(h[e]);
+            acc[2 * e] += f.x;
+            acc[2 * e + 1] += f.y;
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(p.out + (long long)(r0 + j + q) * p.ldo + c) = o;
+      }
+    }
+  }
+  __device__ static __forceinline__ void reduce_unit(const Params& p, int tile_i, int part, int lane) {
+    const int num_n = p.core.num_n_blocks;
+    const int blk = tile_i / num_n, n_blk = tile_i - blk * num_n;
+    const int r0 = blk * BM + part * 8;
+    const long long c = (long long)n_blk * BN + lane * 8;      // one 16-byte vector per lane and row
+    switch (p.P) {
+      case 1: reduce_rows<1, 8>(p, r0, c); break;
+      case 2: reduce_rows<2, 8>(p, r0, c); break;
+      case 4: reduce_rows<4, 4>(p, r0, c); break;
+      case 8: reduce_rows<8, 2>(p, r0, c); break;
+      default: {
+        const long long N = p.core.N;
+        for (int j = 0; j < 8; ++j) {
           float acc[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+          for (int s = 0; s < p.P; ++s) {
+            uint4 x = ptx::ld_relaxed_v4(p.staging_local + ((long long)s * p.rows_per_owner + r0 + j) * N + c);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
 #pragma unroll
-          for (int s = 0; s < kMaxPes; ++s) {
-            if (s < p.P) {
-              uint4 x = ptx::ld_relaxed_v4(p.staging_local + ((long long)s * p.rows_per_owner + r) * N + c);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float2 f = __bfloat1622float2(h[e]);
-                acc[2 * e] += f.x;
-                acc[2 * e + 1] += f.y;
-              }
-            }
+            for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
           }
           uint4 o;
           o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
           o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
-          *reinterpret_cast<uint4*>(p.out + (long long)r * p.ldo + c) = o;
+          *reinterpret_cast<uint4*>(p.out + (long long)(r0 + j) * p.ldo + c) = o;
         }
       }
-      __syncthreads();
     }
+  }
+  // Tail: claims the next `want` units and reduces them, waiting (bounded) for their partials.  Only
+  // called by a CTA that has finished all its tiles, so nobody can be waiting for this CTA in turn.
+  __device__ static __forceinline__ bool claim_and_reduce(const Params& p, int lane, Guard& g, int want) {
+    const int total = p.blocks_per_owner * p.core.num_n_blocks * kUnitsPerTile;
+    unsigned int* ctr = p.ticket + (p.call & 1);
+    unsigned int t0 = 0;
+    if (lane == 0) t0 = atomicAdd(ctr, (unsigned)want);
+    t0 = __shfl_sync(0xffffffffu, t0, 0);
+    if ((int)t0 >= total) return false;
+    int waited_tile = -1;
+    for (int t = (int)t0; t < (int)t0 + want && t < total; ++t) {
+      const int tile_i = t / kUnitsPerTile, part = t - tile_i * kUnitsPerTile;
+      if (tile_i != waited_tile) {
+        int ok = 1;
+        if (lane == 0) ok = wait_ge<true>(p.sig_local + tile_i, p.expect, g, ERR_PEER_SIGNAL) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return false;
+        waited_tile = tile_i;
+      }
+      reduce_unit(p, tile_i, part, lane);
+    }
+    return true;
+  }
+  // During the GEMM: take the next unit only if its partials are already complete.  This must never
+  // block — the warp still owes its CTA an epilogue, and a CTA whose epilogue warps wait for another
+  // CTA's tile while that CTA waits for theirs would deadlock — so the unit is claimed with a
+  // compare-and-swap on the counter value whose readiness was just checked.
+  __device__ static __forceinline__ bool try_reduce_ready_unit(const Params& p, int lane) {
+    const int total = p.blocks_per_owner * p.core.num_n_blocks * kUnitsPerTile;
+    unsigned int* ctr = p.ticket + (p.call & 1);
+    int got = 0;
+    unsigned int t = 0;
+    if (lane == 0) {
+      t = *reinterpret_cast<volatile unsigned int*>(ctr);
+      if ((int)t < total) {
+        unsigned long long v = ptx::ld_acquire_sys_u64(reinterpret_cast<const uint64_t*>(p.sig_local + t / kUnitsPerTile));
+        if (v >= p.expect && atomicCAS(ctr, t, t + 1) == t) got = 1;
+      }
+    }
+    got = __shfl_sync(0xffffffffu, got, 0);
+    if (!got) return false;
+    t = __shfl_sync(0xffffffffu, t, 0);
+    const int tile_i = t / kUnitsPerTile;
+    reduce_unit(p, tile_i, (int)t - tile_i * kUnitsPerTile, lane);
+    return true;
+  }
+  __device__ static __forceinline__ void prologue(const Params& p, Guard&) {
+    if (blockIdx.x == 0) p.ticket[(p.call + 1) & 1] = 0;      // recycle the other parity's counter
+  }
+  // While the tensor core works on a tile of sub-round s, the epilogue warps reduce units of the
+  // sub-rounds before s, whose partials have been sent by every rank.
+  __device__ static __forceinline__ bool idle_work(const Params& p, int, int lane, Guard&, int) {
+    if (p.tune & 1) return false;
+    return try_reduce_ready_unit(p, lane);
+  }
+  // After the CTA's last tile every warp keeps claiming units until none is left.
+  __device__ static __forceinline__ void tail(const Params& p, const Smem&, Guard& g) {
+    const int lane = threadIdx.x & 31;
+    if (p.tune & 2) return;
+    while (claim_and_reduce(p, lane, g, 4)) {}
   }
 };
 
@@ -209,7 +299,7 @@ struct AgGemm : PolicyDefaults {
     return true;
   }
   // A warp pulls one piece (<= 16 KiB of one row) of a peer's rows into the local gathered buffer.
-  __device__ static __forceinline__ bool idle_work(const Params& p, int, int lane, Guard& g) {
+  __device__ static __forceinline__ bool idle_work(const Params& p, int, int lane, Guard& g, int = 0) {
     if (p.P == 1) return false;
     unsigned int t = 0;
     if (lane == 0) t = atomicAdd(&p.ticket[p.call & 1], 1u);
@@ -250,7 +340,7 @@ struct AgGemm : PolicyDefaults {
     return true;
   }
   __device__ static __forceinline__ void epilogue_drain(const Params& p, int ew, int lane, Guard& g) {
-    while (idle_work(p, ew, lane, g)) {}
+    while (idle_work(p, ew, lane, g, 0)) {}
   }
   // Before the kernel ends, CTA 0 makes sure every peer has finished pulling this rank's rows.
   __device__ static __forceinline__ void tail(const Params& p, const Smem&, Guard& g) {
@@ -333,6 +423,8 @@ int bshmem_fused_rs_plan(const bshmem_dev_state_t* st, int M, int N, int K, void
   p->sig_local = static_cast<unsigned long long*>(sig_local);
   int rc = common_init(p);
   if (rc) { delete p; return rc; }
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->ticket, sizeof(unsigned int) * 2));
+  BSHMEM_CUDA_TRY(cudaMemset(p->ticket, 0, sizeof(unsigned int) * 2));
   *out = p;
   return 0;
 }
@@ -372,6 +464,9 @@ int bshmem_fused_rs_run(void* plan, const void* x, int ldx, const void* w, int l
   prm.staging_local = reinterpret_cast<const __nv_bfloat16*>(stage_par);
   prm.out = static_cast<__nv_bfloat16*>(out);
   prm.ldo = ldo;
+  prm.ticket = p->ticket;
+  prm.call = p->call;
+  { const char* t = getenv("B200SHMEM_RS_TUNE"); prm.tune = t ? atoi(t) : 0; }
   int tiles = prm.core.num_m_blocks * prm.core.num_n_blocks;
   int ctas = p->sms;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;

@@ -169,7 +169,8 @@ struct PolicyDefaults {
   }
   template <class Params> __device__ static __forceinline__ void tile_done(const Params&, int, int, int, int) {}
   // work for an epilogue warp while the tensor core is busy; false = nothing to do
-  template <class Params> __device__ static __forceinline__ bool idle_work(const Params&, int, int, Guard&) { return false; }
+  // `tile` is the tile this CTA is working on (lets a policy order its side work by schedule progress)
+  template <class Params> __device__ static __forceinline__ bool idle_work(const Params&, int, int, Guard&, int) { return false; }
   // after an epilogue warp's last tile
   template <class Params> __device__ static __forceinline__ void epilogue_drain(const Params&, int, int, Guard&) {}
   // whole CTA, after all roles have finished (before TMEM is released)
@@ -287,7 +288,7 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       P::tile_coords(prm, tile, &m_blk, &n_blk);
       // the tensor core is busy with this tile: do useful work until the accumulator is ready
       while (!ptx::mbar_try_wait(L.tmem_full(half), acc_ph)) {
-        if (!P::idle_work(prm, ew, lane, g)) {
+        if (!P::idle_work(prm, ew, lane, g, tile)) {
           if (!mbar_wait(L.tmem_full(half), acc_ph, g, ERR_EPI_TMEM_FULL)) ok = false;
           break;
         }

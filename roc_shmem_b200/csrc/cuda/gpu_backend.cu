@@ -525,6 +525,18 @@ int bshmem_gpu_init(void* heap, const bshmem_config_t* cfg, int coll_ctas, int o
   if (c.timeout_us == 0) c.timeout_us = 30ull * 1000 * 1000;
   auto* be = new GpuBackend(static_cast<gpu::Heap*>(heap), own_heap != 0);
   int rc = be->setup(c, coll_ctas);
+  // Load every kernel of this library now.  With lazy module loading the first launch of a kernel
+  // can need a device-wide quiet point; if that first launch came from the proxy thread while a user
+  // kernel is spinning on the proxy's answer, neither would ever finish.
+  {
+    cudaFuncAttributes fa;
+    cudaFuncGetAttributes(&fa, k_amo);
+    cudaFuncGetAttributes(&fa, k_wait_until);
+    cudaFuncGetAttributes(&fa, k_signal);
+    cudaFuncGetAttributes(&fa, k_rma);
+    cudaFuncGetAttributes(&fa, k_coll);
+    cudaFuncGetAttributes(&fa, k_coll_group);
+  }
   if (rc != BSHMEM_OK) { g_err = be->last_error(); delete be; return rc; }
   *out = make_runtime(std::unique_ptr<Backend>(be), &c);
   return BSHMEM_OK;

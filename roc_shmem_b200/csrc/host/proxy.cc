@@ -184,7 +184,7 @@ int bshmem_proxy_host_submit(bshmem_proxy_t* px, const bshmem_proxy_desc_t* cmd,
   slot->ticket = ticket;
   __atomic_store_n(&slot->valid, ticket + 1, __ATOMIC_RELEASE);
   if (!(cmd->flags & BSHMEM_PROXY_FLAG_BLOCKING)) return BSHMEM_OK;
-  for (unsigned spins = 0; __atomic_load_n(&r.completion[ticket & mask], __ATOMIC_ACQUIRE) != ticket + 1; ++spins) {
+  for (unsigned spins = 0; __atomic_load_n(&r.completion[ticket & mask], __ATOMIC_ACQUIRE) < ticket + 1; ++spins) {
     if ((spins & 255) == 255 && now_ns() > deadline) return BSHMEM_ERR_TIMEOUT;
     backoff(spins);
   }
