@@ -164,66 +164,53 @@ struct GemmRs : PolicyDefaults {
       }
     }
   }
-  // Tail: claims the next `want` units and reduces them, waiting (bounded) for their partials.  Only
-  // called by a CTA that has finished all its tiles, so nobody can be waiting for this CTA in turn.
-  __device__ static __forceinline__ bool claim_and_reduce(const Params& p, int lane, Guard& g, int want) {
+  // Units are dealt out statically: epilogue warp w of CTA c owns units c*8+w, c*8+w + G*8, ... (G = grid
+  // size), in tile order, which is also the order in which the partials arrive.  Its cursor (how many of
+  // its units are done) lives in the warp's state word, so no atomics and no contention are involved.
+  __device__ static __forceinline__ int unit_of(const Params& p, int ew, int k) {
+    return k * (int)gridDim.x * NUM_EPI_WARPS + (int)blockIdx.x * NUM_EPI_WARPS + ew;
+  }
+  // During the GEMM: reduce my next unit only if its partials are already complete.  This must never
+  // block — the warp still owes its CTA an epilogue, and two CTAs whose epilogue warps wait for each
+  // other's current tile would deadlock.
+  __device__ static __forceinline__ bool idle_work(const Params& p, int ew, int lane, Guard&, int, volatile int* cursor) {
+    if (p.tune & 1) return false;
     const int total = p.blocks_per_owner * p.core.num_n_blocks * kUnitsPerTile;
-    unsigned int* ctr = p.ticket + (p.call & 1);
-    unsigned int t0 = 0;
-    if (lane == 0) t0 = atomicAdd(ctr, (unsigned)want);
-    t0 = __shfl_sync(0xffffffffu, t0, 0);
-    if ((int)t0 >= total) return false;
+    const int k = *cursor;
+    const int u = unit_of(p, ew, k);
+    if (u >= total) return false;
+    const int tile_i = u / kUnitsPerTile;
+    int ready = 0;
+    if (lane == 0) ready = ptx::ld_acquire_sys_u64(reinterpret_cast<const uint64_t*>(p.sig_local + tile_i)) >= p.expect;
+    ready = __shfl_sync(0xffffffffu, ready, 0);
+    if (!ready) return false;
+    reduce_unit(p, tile_i, u - tile_i * kUnitsPerTile, lane);
+    __syncwarp();
+    if (lane == 0) *cursor = k + 1;
+    __syncwarp();
+    return true;
+  }
+  // After the CTA's last tile its epilogue warps finish their remaining units, waiting (bounded) for the
+  // partials; nobody can be waiting for this CTA any more.
+  __device__ static __forceinline__ void tail(const Params& p, const Smem& L, Guard& g) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp < 2 || (p.tune & 2)) return;
+    const int ew = warp - 2;
+    const int total = p.blocks_per_owner * p.core.num_n_blocks * kUnitsPerTile;
     int waited_tile = -1;
-    for (int t = (int)t0; t < (int)t0 + want && t < total; ++t) {
-      const int tile_i = t / kUnitsPerTile, part = t - tile_i * kUnitsPerTile;
+    for (int k = *L.warp_state(warp);; ++k) {
+      const int u = unit_of(p, ew, k);
+      if (u >= total) break;
+      const int tile_i = u / kUnitsPerTile;
       if (tile_i != waited_tile) {
         int ok = 1;
         if (lane == 0) ok = wait_ge<true>(p.sig_local + tile_i, p.expect, g, ERR_PEER_SIGNAL) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) return false;
+        if (!ok) break;
         waited_tile = tile_i;
       }
-      reduce_unit(p, tile_i, part, lane);
+      reduce_unit(p, tile_i, u - tile_i * kUnitsPerTile, lane);
     }
-    return true;
-  }
-  // During the GEMM: take the next unit only if its partials are already complete.  This must never
-  // block — the warp still owes its CTA an epilogue, and a CTA whose epilogue warps wait for another
-  // CTA's tile while that CTA waits for theirs would deadlock — so the unit is claimed with a
-  // compare-and-swap on the counter value whose readiness was just checked.
-  __device__ static __forceinline__ bool try_reduce_ready_unit(const Params& p, int lane) {
-    const int total = p.blocks_per_owner * p.core.num_n_blocks * kUnitsPerTile;
-    unsigned int* ctr = p.ticket + (p.call & 1);
-    int got = 0;
-    unsigned int t = 0;
-    if (lane == 0) {
-      t = *reinterpret_cast<volatile unsigned int*>(ctr);
-      if ((int)t < total) {
-        unsigned long long v = ptx::ld_acquire_sys_u64(reinterpret_cast<const uint64_t*>(p.sig_local + t / kUnitsPerTile));
-        if (v >= p.expect && atomicCAS(ctr, t, t + 1) == t) got = 1;
-      }
-    }
-    got = __shfl_sync(0xffffffffu, got, 0);
-    if (!got) return false;
-    t = __shfl_sync(0xffffffffu, t, 0);
-    const int tile_i = t / kUnitsPerTile;
-    reduce_unit(p, tile_i, (int)t - tile_i * kUnitsPerTile, lane);
-    return true;
-  }
-  __device__ static __forceinline__ void prologue(const Params& p, Guard&) {
-    if (blockIdx.x == 0) p.ticket[(p.call + 1) & 1] = 0;      // recycle the other parity's counter
-  }
-  // While the tensor core works on a tile of sub-round s, the epilogue warps reduce units of the
-  // sub-rounds before s, whose partials have been sent by every rank.
-  __device__ static __forceinline__ bool idle_work(const Params& p, int, int lane, Guard&, int) {
-    if (p.tune & 1) return false;
-    return try_reduce_ready_unit(p, lane);
-  }
-  // After the CTA's last tile every warp keeps claiming units until none is left.
-  __device__ static __forceinline__ void tail(const Params& p, const Smem&, Guard& g) {
-    const int lane = threadIdx.x & 31;
-    if (p.tune & 2) return;
-    while (claim_and_reduce(p, lane, g, 4)) {}
   }
 };
 
@@ -299,7 +286,7 @@ struct AgGemm : PolicyDefaults {
     return true;
   }
   // A warp pulls one piece (<= 16 KiB of one row) of a peer's rows into the local gathered buffer.
-  __device__ static __forceinline__ bool idle_work(const Params& p, int, int lane, Guard& g, int = 0) {
+  __device__ static __forceinline__ bool idle_work(const Params& p, int, int lane, Guard& g, int = 0, volatile int* = nullptr) {
     if (p.P == 1) return false;
     unsigned int t = 0;
     if (lane == 0) t = atomicAdd(&p.ticket[p.call & 1], 1u);

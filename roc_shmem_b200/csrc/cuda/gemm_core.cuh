@@ -133,6 +133,10 @@ struct Smem {
     return reinterpret_cast<volatile int*>(gen + SMEM_TILES + 8 * (2 * STAGES + 4) + 8);
   }
   // 16 bytes of policy scratch (e.g. a broadcast slot for the tail phase)
+  // one word of private state per warp (10 warps), zeroed at kernel start
+  __device__ __forceinline__ volatile int* warp_state(int w) const {
+    return reinterpret_cast<volatile int*>(gen + SMEM_TILES + 128 + 4 * w);
+  }
   __device__ __forceinline__ volatile int* scratch() const {
     return reinterpret_cast<volatile int*>(gen + SMEM_TILES + 8 * (2 * STAGES + 4) + 16);
   }
@@ -159,6 +163,18 @@ struct PolicyDefaults {
   // matching up-projections; the epilogue writes silu(gate) * up, i.e. half as many output columns.
   static constexpr bool kGated = false;
   template <class Params> __device__ static __forceinline__ int b_row(const Params&, int, int n_blk) { return n_blk * BN; }
+  // K-major operands: one TMA box per operand and stage (256 rows x 128 bytes of K) ...
+  template <class Params>
+  __device__ static __forceinline__ void load_stage(const Params&, const CUtensorMap* ma, const CUtensorMap* mb, uint32_t a_smem,
+                                                    uint32_t b_smem, uint32_t bar, int k_elem, int a_row, int b_row) {
+    ptx::tma_load_2d(a_smem, ma, bar, k_elem, a_row);
+    ptx::tma_load_2d(b_smem, mb, bar, k_elem, b_row);
+  }
+  // ... and shared-memory descriptors that step 32 bytes along K inside the swizzle atom.
+  __device__ static __forceinline__ uint64_t desc_a(uint32_t a0, int half, int k) {
+    return ptx::umma_desc_sw128(a0 + half * (UMMA_M * BK_BYTES) + k * UMMA_K_BYTES);
+  }
+  __device__ static __forceinline__ uint64_t desc_b(uint32_t b0, int k) { return ptx::umma_desc_sw128(b0 + k * UMMA_K_BYTES); }
   template <class Params> __device__ static __forceinline__ bool a_ready(const Params&, int, Guard&) { return true; }
   // k-blocks of the tile's reduction (ragged per group in the grouped weight-gradient GEMM)
   template <class Params> __device__ static __forceinline__ int num_kb(const Params& p, int, int bk) {
@@ -170,7 +186,7 @@ struct PolicyDefaults {
   template <class Params> __device__ static __forceinline__ void tile_done(const Params&, int, int, int, int) {}
   // work for an epilogue warp while the tensor core is busy; false = nothing to do
   // `tile` is the tile this CTA is working on (lets a policy order its side work by schedule progress)
-  template <class Params> __device__ static __forceinline__ bool idle_work(const Params&, int, int, Guard&, int) { return false; }
+  template <class Params> __device__ static __forceinline__ bool idle_work(const Params&, int, int, Guard&, int, volatile int*) { return false; }
   // after an epilogue warp's last tile
   template <class Params> __device__ static __forceinline__ void epilogue_drain(const Params&, int, int, Guard&) {}
   // whole CTA, after all roles have finished (before TMEM is released)
@@ -201,6 +217,7 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
 
   if (threadIdx.x == 0) {
     *L.abort_flag() = 0;
+    for (int w = 0; w < NUM_THREADS / 32; ++w) *L.warp_state(w) = 0;
     for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(L.full(s), 1); ptx::mbar_init(L.empty(s), 1); }
     for (int h = 0; h < 2; ++h) { ptx::mbar_init(L.tmem_full(h), 1); ptx::mbar_init(L.tmem_empty(h), NUM_EPI_WARPS / 2); }
     ptx::fence_mbar_init();
@@ -233,8 +250,7 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(L.empty(s), ph ^ 1, g, ERR_PRODUCER_EMPTY)) { ok = false; break; }
           ptx::mbar_arrive_expect_tx(L.full(s), STAGE_BYTES);
-          ptx::tma_load_2d(L.a(s), P::map_a(prm), L.full(s), kb * BK, a_row);
-          ptx::tma_load_2d(L.b(s), P::map_b(prm), L.full(s), kb * BK, b_row);
+          P::load_stage(prm, P::map_a(prm),P::map_b(prm), L.a(s), L.b(s), L.full(s), kb * BK, a_row, b_row);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -262,8 +278,8 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
           for (int half = 0; half < 2; ++half) {
 #pragma unroll
             for (int k = 0; k < BK_BYTES / UMMA_K_BYTES; ++k) {
-              uint64_t da = ptx::umma_desc_sw128(a0 + half * (UMMA_M * BK_BYTES) + k * UMMA_K_BYTES);
-              uint64_t db = ptx::umma_desc_sw128(b0 + k * UMMA_K_BYTES);
+              uint64_t da = P::desc_a(a0, half, k);
+              uint64_t db = P::desc_b(b0, k);
               P::mma(tmem_base + half * UMMA_N, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             }
           }
@@ -288,7 +304,7 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       P::tile_coords(prm, tile, &m_blk, &n_blk);
       // the tensor core is busy with this tile: do useful work until the accumulator is ready
       while (!ptx::mbar_try_wait(L.tmem_full(half), acc_ph)) {
-        if (!P::idle_work(prm, ew, lane, g, tile)) {
+        if (!P::idle_work(prm, ew, lane, g, tile, L.warp_state(warp))) {
           if (!mbar_wait(L.tmem_full(half), acc_ph, g, ERR_EPI_TMEM_FULL)) ok = false;
           break;
         }

@@ -383,8 +383,8 @@ class GpuBackend final : public Backend {
     a.psync_off = g.psync_off;
     a.use_nvls = use_nvls_ ? 1 : 0;
     int ctas = 1;
-    if (g.slot >= 0 && bytes > (256u << 10)) {
-      ctas = (int)((bytes + (256u << 10) - 1) / (256u << 10));
+    if (g.slot >= 0 && bytes > (32u << 10)) {   // one CTA per 32 KiB: remote latency, not bandwidth, bounds a CTA
+      ctas = (int)((bytes + (32u << 10) - 1) / (32u << 10));
       if (ctas > coll_ctas_) ctas = coll_ctas_;
     }
     k_coll<<<ctas, 512, 0, stream_>>>(state_, team_of(g), a, dstatus_);

@@ -29,6 +29,7 @@ struct GroupedParams {
   int G, fixed_rows;
   int a_blocks_per_group;          // 256-row blocks between consecutive groups in A and C
   int b_rows_per_group;            // rows between consecutive groups in B
+  int k_rows_per_group;            // token rows between consecutive groups of A and B (transposed-operand mode)
   int group_m;
   int P;                           // arrival wait: number of words, 0 = no wait
   const unsigned long long* arrive;
@@ -94,6 +95,35 @@ struct Grouped : PolicyDefaults {
   }
 };
 
+// Weight-gradient flavour: C_g[M, N] = A_g^T · B_g with A_g stored [tokens_g][M] and B_g stored [tokens_g][N]
+// (the token-major activations as they are), i.e. both operands MN-major; the reduction runs over the
+// ragged token dimension.  A stage holds, per operand, four 64-wide MN blocks of 64 tokens each (8 KiB per
+// block, 128-byte swizzle): inside a block 8 tokens form one 1 KiB swizzle atom (SBO), blocks are 8 KiB apart
+// (LBO).  Tokens in [count, next multiple of 64) of every group must be zero (bshmem_moe_zero_pad_rows).
+struct GroupedTN : Grouped<false> {
+  static constexpr uint32_t kIdesc = ptx::umma_idesc_mn_major(1, 1, UMMA_M, UMMA_N);
+  static constexpr uint32_t kBlock = 64 * BK_BYTES;            // one 64 (MN) x 64 (tokens) block: 8 KiB
+  // the "row" values handed to load_stage are the tile's block indices; the token row comes from the group
+  __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk; }
+  __device__ static __forceinline__ int b_row(const Params&, int, int n_blk) { return n_blk; }
+  __device__ static __forceinline__ void load_stage(const Params& p, const CUtensorMap* ma, const CUtensorMap* mb, uint32_t a_smem,
+                                                    uint32_t b_smem, uint32_t bar, int k_elem, int m_blk, int n_blk) {
+    const int g = m_blk / p.a_blocks_per_group;
+    const int tok = g * p.k_rows_per_group + k_elem;
+    const int m0 = (m_blk - g * p.a_blocks_per_group) * BM, n0 = n_blk * BN;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      ptx::tma_load_2d(a_smem + i * kBlock, ma, bar, m0 + i * 64, tok);
+      ptx::tma_load_2d(b_smem + i * kBlock, mb, bar, n0 + i * 64, tok);
+    }
+  }
+  // one MMA consumes 16 tokens = two swizzle atoms (2 KiB) of every MN block
+  __device__ static __forceinline__ uint64_t desc_a(uint32_t a0, int half, int k) {
+    return ptx::umma_desc_sw128_ex(a0 + half * 2 * kBlock + k * 2048, kBlock, 1024);
+  }
+  __device__ static __forceinline__ uint64_t desc_b(uint32_t b0, int k) { return ptx::umma_desc_sw128_ex(b0 + k * 2048, kBlock, 1024); }
+};
+
 __global__ void __launch_bounds__(NUM_THREADS, 1) grouped_gemm_kernel(const __grid_constant__ GroupedParams prm) {
   extern __shared__ uint8_t smem_raw[];
   gemm_mainloop<Grouped<false>>(prm, smem_raw);
@@ -101,6 +131,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) grouped_gemm_kernel(const __gr
 __global__ void __launch_bounds__(NUM_THREADS, 1) grouped_gemm_gated_kernel(const __grid_constant__ GroupedParams prm) {
   extern __shared__ uint8_t smem_raw[];
   gemm_mainloop<Grouped<true>>(prm, smem_raw);
+}
+__global__ void __launch_bounds__(NUM_THREADS, 1) grouped_gemm_tn_kernel(const __grid_constant__ GroupedParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_mainloop<GroupedTN>(prm, smem_raw);
+}
+
+// Zero the token rows [count_g, next multiple of 64) of every group of a [G][cap][cols] bf16 buffer.
+__global__ void zero_pad_rows_kernel(__nv_bfloat16* buf, const int* counts, int cap, int cols) {
+  const int g = blockIdx.y;
+  const int c = counts[g];
+  int end = (c + 63) / 64 * 64;
+  if (end > cap) end = cap;
+  const int vec_per_row = cols / 8;
+  const long long n = (long long)(end - c) * vec_per_row;
+  uint4* base = reinterpret_cast<uint4*>(buf + ((size_t)g * cap + c) * cols);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    base[i] = make_uint4(0, 0, 0, 0);
 }
 
 int* g_err_dev[64] = {};
@@ -113,6 +160,7 @@ int ensure(int dev) {
   BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_gated_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
   return 0;
 }
 
@@ -160,6 +208,52 @@ int bshmem_moe_grouped_gemm(const void* A, const void* B, void* C, int G, int a_
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (gated) grouped_gemm_gated_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
   else grouped_gemm_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// Weight-gradient GEMM on token-major operands: C_g[M, N] = A_g^T · B_g for every group.
+//   A: [G * cap, M] (lda), B: [G * cap, N] (ldb), C: [G * M, N] (ldc); the number of tokens of group g is
+//   klen_dev[g] (<= cap).  Token rows [klen, next multiple of 64) must be zero in A and B.
+int bshmem_moe_grouped_gemm_tn(const void* A, const void* B, void* C, int G, int cap, int M, int N, int lda, int ldb, int ldc,
+                               const int* klen_dev, void* stream, int timeout_ms, int max_ctas) {
+  if (G < 1 || M % BM || N % BN || cap % 64 || lda % 8 || ldb % 8 || ldc % 8 || !klen_dev) {
+    host::last_error() = "grouped gemm (transposed operands): needs M % 256 == 0, N % 256 == 0, capacity % 64 == 0, leading dimensions % 8 == 0";
+    return 1;
+  }
+  int dev = 0;
+  BSHMEM_CUDA_TRY(cudaGetDevice(&dev));
+  int rc = ensure(dev);
+  if (rc) return rc;
+  GroupedParams p;
+  memset(&p, 0, sizeof(p));
+  p.core.M = G * M; p.core.N = N; p.core.K = cap;
+  p.core.num_m_blocks = p.core.M / BM; p.core.num_n_blocks = N / BN;
+  p.core.group_m = 16;
+  p.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 4000) * 1000000ull;
+  p.core.err = g_err_dev[dev];
+  p.rows = nullptr; p.klen = klen_dev; p.G = G; p.fixed_rows = M;
+  p.a_blocks_per_group = M / BM;
+  p.k_rows_per_group = cap;
+  p.group_m = 16;
+  // boxes of 64 MN-elements (128 bytes, the swizzle span) by 64 tokens
+  rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)G * cap, M, lda, 64, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, (uint64_t)G * cap, N, ldb, 64, 64);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&p.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, (uint64_t)G * M, N, ldc, 32, EPI_COLS);
+  if (rc) return rc;
+  int ctas = g_sms[dev];
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  grouped_gemm_tn_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// buf: [G][cap][cols] bf16, cols % 8 == 0: zero rows [counts[g], next multiple of 64) of every group.
+int bshmem_moe_zero_pad_rows(void* buf, const int* counts_dev, int G, int cap, int cols, void* stream) {
+  if (cols % 8 || G < 1) { host::last_error() = "zero_pad_rows: cols % 8 != 0"; return 1; }
+  zero_pad_rows_kernel<<<dim3(8, G), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(buf), counts_dev, cap, cols);
   BSHMEM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

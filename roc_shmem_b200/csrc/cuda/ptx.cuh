@@ -164,10 +164,27 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// General form: 128-byte swizzle with explicit leading / stride byte offsets (used for MN-major tiles:
+// 64 MN-elements x 8 K-rows per swizzle atom, LBO = distance between 64-wide MN blocks, SBO = distance
+// between groups of 8 K-rows).
+__device__ __forceinline__ uint64_t umma_desc_sw128_ex(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // Instruction descriptor, kind::f16 / kind::f8f6f4: fp32 accumulate, both operands K-major.
 //   a_fmt/b_fmt: kind::f16: 0 = f16, 1 = bf16;  kind::f8f6f4: 0 = e4m3, 1 = e5m2.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n) {
   return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// Same with both operands MN-major (bits 15 and 16): A is stored [K][M], B is stored [K][N].
+__host__ __device__ constexpr uint32_t umma_idesc_mn_major(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n) {
+  return umma_idesc(a_fmt, b_fmt, m, n) | (1u << 15) | (1u << 16);
 }
 
 // ---- system-scope accesses for peer (NVLink) memory -----------------------------------

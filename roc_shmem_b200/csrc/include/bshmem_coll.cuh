@@ -155,9 +155,10 @@ template <typename T> union Vec16 {
 
 // dst[i] = reduce over members k (in team order) of src_k[i], for i in [begin, end) elements;
 // the result goes to `ndst` destinations.  Vector body + scalar edges, striped over the block.
-template <typename T>
-__device__ __forceinline__ void reduce_range(int op, int nsrc, const T* const* srcs, int ndst, T* const* dsts,
-                                             size_t begin, size_t end) {
+template <typename T, int OP>
+__device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, int ndst, T* const* dsts,
+                                                size_t begin, size_t end) {
+  constexpr int op = OP;      // compile-time operator: the per-element switch in apply() folds away
   using A = typename Acc<T>::type;
   constexpr int VE = 16 / sizeof(T);
   const int tid = threadIdx.x, nth = blockDim.x;
@@ -171,15 +172,20 @@ __device__ __forceinline__ void reduce_range(int op, int nsrc, const T* const* s
     for (int d = 0; d < ndst; ++d) dsts[d][i] = from_acc<T>(acc);
   }
   for (size_t v = vbeg / VE + tid; v < vend / VE; v += nth) {
-    Vec16<T> in;
+    // issue every member's load before the first use: up to 16 peer loads in flight per thread
+    Vec16<T> in[BSHMEM_MAX_PES];
+#pragma unroll
+    for (int k = 0; k < BSHMEM_MAX_PES; ++k)
+      if (k < nsrc) in[k].raw = reinterpret_cast<const uint4*>(srcs[k])[v];
     A acc[VE];
-    in.raw = reinterpret_cast<const uint4*>(srcs[0])[v];
 #pragma unroll
-    for (int e = 0; e < VE; ++e) acc[e] = to_acc<T>(in.e[e]);
-    for (int k = 1; k < nsrc; ++k) {
-      in.raw = reinterpret_cast<const uint4*>(srcs[k])[v];
+    for (int e = 0; e < VE; ++e) acc[e] = to_acc<T>(in[0].e[e]);
 #pragma unroll
-      for (int e = 0; e < VE; ++e) acc[e] = apply<A>(op, acc[e], to_acc<T>(in.e[e]));
+    for (int k = 1; k < BSHMEM_MAX_PES; ++k) {
+      if (k < nsrc) {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) acc[e] = apply<A>(op, acc[e], to_acc<T>(in[k].e[e]));
+      }
     }
     Vec16<T> out;
 #pragma unroll
@@ -191,6 +197,24 @@ __device__ __forceinline__ void reduce_range(int op, int nsrc, const T* const* s
     A acc = to_acc<T>(srcs[0][i]);
     for (int k = 1; k < nsrc; ++k) acc = apply<A>(op, acc, to_acc<T>(srcs[k][i]));
     for (int d = 0; d < ndst; ++d) dsts[d][i] = from_acc<T>(acc);
+  }
+}
+
+// Run-time operator -> compile-time instantiation (bitwise operators exist for integer types only).
+template <typename T>
+__device__ __forceinline__ void reduce_range(int op, int nsrc, const T* const* srcs, int ndst, T* const* dsts,
+                                             size_t begin, size_t end) {
+  switch (op) {
+    case BSHMEM_SUM: reduce_range_op<T, BSHMEM_SUM>(nsrc, srcs, ndst, dsts, begin, end); break;
+    case BSHMEM_MIN: reduce_range_op<T, BSHMEM_MIN>(nsrc, srcs, ndst, dsts, begin, end); break;
+    case BSHMEM_MAX: reduce_range_op<T, BSHMEM_MAX>(nsrc, srcs, ndst, dsts, begin, end); break;
+    case BSHMEM_PROD: reduce_range_op<T, BSHMEM_PROD>(nsrc, srcs, ndst, dsts, begin, end); break;
+    default:
+      if constexpr (!std::is_floating_point<typename Acc<T>::type>::value) {
+        if (op == BSHMEM_AND) reduce_range_op<T, BSHMEM_AND>(nsrc, srcs, ndst, dsts, begin, end);
+        else if (op == BSHMEM_OR) reduce_range_op<T, BSHMEM_OR>(nsrc, srcs, ndst, dsts, begin, end);
+        else reduce_range_op<T, BSHMEM_XOR>(nsrc, srcs, ndst, dsts, begin, end);
+      }
   }
 }
 

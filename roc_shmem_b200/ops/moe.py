@@ -53,6 +53,8 @@ def moe_lib() -> C.CDLL:
         f("bshmem_moe_swiglu_bwd", VP, VP, VP, I, I, I, VP, VP)
         f("bshmem_moe_transpose_pad", VP, VP, I, I, I, VP, VP)
         f("bshmem_moe_grouped_gemm", VP, VP, VP, I, I, I, I, I, I, I, I, VP, I, VP, I, VP, VP, I, VP, I, I)
+        f("bshmem_moe_grouped_gemm_tn", VP, VP, VP, I, I, I, I, I, I, I, VP, VP, I, I)
+        f("bshmem_moe_zero_pad_rows", VP, VP, I, I, I, VP)
         f("bshmem_moe_gemm_error_site", I)
         f("bshmem_moe_gemm_error_word", res=VP)
         _declared = True
@@ -91,6 +93,29 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, groups: in
         raise RuntimeError(f"grouped gemm failed ({st}): {lib.bshmem_moe_gemm_last_error().decode()}")
 
 
+def grouped_gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, groups: int, counts: torch.Tensor, *,
+                    timeout_ms: int = 4000, max_ctas: int = 0) -> None:
+    """out_g[M, N] = a_g.T @ b_g per group with token-major operands a: [G*cap, M], b: [G*cap, N] and
+    `counts[g]` tokens per group; both operands go to the tensor core MN-major, no transpose is materialised.
+    Token rows [counts[g], next multiple of 64) of a and b must be zero (see zero_pad_rows)."""
+    lib = moe_lib()
+    G = groups
+    cap = a.shape[0] // G
+    st = lib.bshmem_moe_grouped_gemm_tn(a.data_ptr(), b.data_ptr(), out.data_ptr(), G, cap, a.shape[1], b.shape[1], a.stride(0),
+                                        b.stride(0), out.stride(0), counts.data_ptr(), _stream(), timeout_ms, max_ctas)
+    if st != 0:
+        raise RuntimeError(f"grouped gemm (tn) failed ({st}): {lib.bshmem_moe_gemm_last_error().decode()}")
+
+
+def zero_pad_rows(buf: torch.Tensor, groups: int, counts: torch.Tensor) -> None:
+    """Zero rows [counts[g], next multiple of 64) of every group of a contiguous [G*cap, cols] bf16 buffer."""
+    lib = moe_lib()
+    assert buf.is_contiguous()
+    st = lib.bshmem_moe_zero_pad_rows(buf.data_ptr(), counts.data_ptr(), groups, buf.shape[0] // groups, buf.shape[1], _stream())
+    if st != 0:
+        raise RuntimeError(f"zero_pad_rows failed ({st}): {lib.bshmem_moe_gemm_last_error().decode()}")
+
+
 class MoELayer:
     """One MoE block: y[T, H] = combine(experts(dispatch(x)))  with forward and backward.
 
@@ -99,7 +124,8 @@ class MoELayer:
     `sync_transposes()` (all operands of the tcgen05 kernels are K-major)."""
 
     def __init__(self, rt, hidden: int, ffn: int, n_experts: int, topk: int, max_tokens: int, capacity_factor: float = 1.25,
-                 training: bool = True, timeout_ms: int = 4000):
+                 training: bool = True, timeout_ms: int = 4000, tn_gemm: bool = True):
+        self.tn_gemm = tn_gemm          # weight gradients on MN-major operands (False: explicit transposes)
         self.rt, self.H, self.F, self.E, self.topk, self.T = rt, hidden, ffn, n_experts, topk, max_tokens
         self.lib = moe_lib()
         P = rt.n_pes
@@ -144,8 +170,9 @@ class MoELayer:
             self.dh = torch.empty((G * cap, F), dtype=bf, device=dev)
             self.dgu = torch.empty((G * cap, 2 * F), dtype=bf, device=dev)
             self.dxe = torch.empty((G * cap, H), dtype=bf, device=dev)
-            self.t_a = torch.empty((G * 2 * F * cap,), dtype=bf, device=dev)  # transposed operands, reused
-            self.t_b = torch.empty((G * F * cap,), dtype=bf, device=dev)
+            if not tn_gemm:
+                self.t_a = torch.empty((G * 2 * F * cap,), dtype=bf, device=dev)  # transposed operands, reused
+                self.t_b = torch.empty((G * max(F, H) * cap,), dtype=bf, device=dev)
             self.dw13 = torch.empty((G, 2 * F, H), dtype=bf, device=dev)
             self.dw2 = torch.empty((G, H, F), dtype=bf, device=dev)
             self.dxbuf = rt.empty((n_entries, H), bf, align=1024)
@@ -246,20 +273,30 @@ class MoELayer:
         # d_hact = d_y · W2            (B operand = W2^T [F, H], K = H)
         grouped_gemm(self.recv, self.w2_t.view(G * F, H), self.dh, G, rows=rc, arrive=self._sig_ptr(par, SIG_BWD_DISPATCH),
                      expected=self.expect_from, n_arrive=P, timeout_ms=self.timeout_ms)
-        # dW2 = d_y^T · hact           (A = d_y^T [H, cap], B = hact^T [F, cap], ragged K = tokens)
-        ta = self.t_a[: G * H * cap].view(G * H, cap)
-        tb = self.t_b[: G * F * cap].view(G * F, cap)
-        self._chk(lib.bshmem_moe_transpose_pad(self.recv.data_ptr(), rc.data_ptr(), G, cap, H, ta.data_ptr(), s), "transpose")
-        self._chk(lib.bshmem_moe_transpose_pad(self.hact.data_ptr(), rc.data_ptr(), G, cap, F, tb.data_ptr(), s), "transpose")
-        grouped_gemm(ta, tb, self.dw2.view(G * H, F), G, fixed_rows=H, klen=rc, timeout_ms=self.timeout_ms)
+        # dW2 = d_y^T · hact: token-major operands straight into the MN-major tensor-core path
+        if self.tn_gemm:
+            zero_pad_rows(self.recv, G, rc)
+            zero_pad_rows(self.hact, G, rc)
+            grouped_gemm_tn(self.recv, self.hact, self.dw2.view(G * H, F), G, rc, timeout_ms=self.timeout_ms)
+        else:                          # explicit transposes + ragged-K K-major GEMM
+            ta = self.t_a[: G * H * cap].view(G * H, cap)
+            tb = self.t_b[: G * F * cap].view(G * F, cap)
+            self._chk(lib.bshmem_moe_transpose_pad(self.recv.data_ptr(), rc.data_ptr(), G, cap, H, ta.data_ptr(), s), "transpose")
+            self._chk(lib.bshmem_moe_transpose_pad(self.hact.data_ptr(), rc.data_ptr(), G, cap, F, tb.data_ptr(), s), "transpose")
+            grouped_gemm(ta, tb, self.dw2.view(G * H, F), G, fixed_rows=H, klen=rc, timeout_ms=self.timeout_ms)
         # SwiGLU backward, then dW13 = d_gu^T · x and d_x = d_gu · W13
         self._chk(lib.bshmem_moe_swiglu_bwd(self.gu.data_ptr(), self.dh.data_ptr(), rc.data_ptr(), G, cap, F, self.dgu.data_ptr(), s),
                   "swiglu bwd")
-        ta2 = self.t_a[: G * 2 * F * cap].view(G * 2 * F, cap)
-        tb2 = self.t_b[: G * H * cap].view(G * H, cap)
-        self._chk(lib.bshmem_moe_transpose_pad(self.dgu.data_ptr(), rc.data_ptr(), G, cap, 2 * F, ta2.data_ptr(), s), "transpose")
-        self._chk(lib.bshmem_moe_transpose_pad(self.xsave.data_ptr(), rc.data_ptr(), G, cap, H, tb2.data_ptr(), s), "transpose")
-        grouped_gemm(ta2, tb2, self.dw13.view(G * 2 * F, H), G, fixed_rows=2 * F, klen=rc, timeout_ms=self.timeout_ms)
+        if self.tn_gemm:
+            zero_pad_rows(self.dgu, G, rc)
+            zero_pad_rows(self.xsave, G, rc)
+            grouped_gemm_tn(self.dgu, self.xsave, self.dw13.view(G * 2 * F, H), G, rc, timeout_ms=self.timeout_ms)
+        else:
+            ta2 = self.t_a[: G * 2 * F * cap].view(G * 2 * F, cap)
+            tb2 = self.t_b[: G * H * cap].view(G * H, cap)
+            self._chk(lib.bshmem_moe_transpose_pad(self.dgu.data_ptr(), rc.data_ptr(), G, cap, 2 * F, ta2.data_ptr(), s), "transpose")
+            self._chk(lib.bshmem_moe_transpose_pad(self.xsave.data_ptr(), rc.data_ptr(), G, cap, H, tb2.data_ptr(), s), "transpose")
+            grouped_gemm(ta2, tb2, self.dw13.view(G * 2 * F, H), G, fixed_rows=2 * F, klen=rc, timeout_ms=self.timeout_ms)
         grouped_gemm(self.dgu, self.w13_t.view(G * H, 2 * F), self.dxe, G, rows=rc, timeout_ms=self.timeout_ms)
         self.launches += 4
         # dispatch-backward = combine of the d_x rows back to their source entries, summed over k

@@ -32,7 +32,12 @@ class RowParallelLinear:
             raise ValueError("token count must divide by the number of PEs")
         dev = rt.device
         self.weight = torch.empty((self.N, self.K), dtype=dtype, device=dev)
-        self.x_dev = torch.empty((self.M, self.K), dtype=dtype, device=dev)
+        # double-buffered device inputs + a copy stream: the host->device copy of step i+1 overlaps step i
+        self.x_bufs = [torch.empty((self.M, self.K), dtype=dtype, device=dev) for _ in range(2)]
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self.copied = [torch.cuda.Event() for _ in range(2)]
+        self.consumed = [torch.cuda.Event() for _ in range(2)]
+        self._step = 0
         self.metric_dev = torch.zeros(1, dtype=torch.float32, device=dev)
         self._launches = 0
         if self.P == 1:
@@ -56,11 +61,21 @@ class RowParallelLinear:
     __call__ = forward
 
     def step_from_host(self, x_host: torch.Tensor, metric_host: torch.Tensor) -> None:
-        """One serving-style step: pinned host activations -> device, layer, one scalar back."""
-        self.x_dev.copy_(x_host, non_blocking=True)
-        y = self.forward(self.x_dev)
+        """One serving-style step: pinned host activations -> device (copy stream, double-buffered so that
+        the copy of the next step overlaps this step's kernel), the layer, one scalar of the result back."""
+        i = self._step & 1
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(self.copy_stream):
+            if self._step >= 2:
+                self.copy_stream.wait_event(self.consumed[i])     # the kernel that read this buffer is done
+            self.x_bufs[i].copy_(x_host, non_blocking=True)
+            self.copied[i].record(self.copy_stream)
+        main.wait_event(self.copied[i])
+        y = self.forward(self.x_bufs[i])
+        self.consumed[i].record(main)
         torch.mean(y, dtype=torch.float32, out=self.metric_dev[0])
         metric_host.copy_(self.metric_dev, non_blocking=True)
+        self._step += 1
 
     def reset_launch_count(self) -> None:
         self._launches = 0

@@ -7,10 +7,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _mk_layer(rt, T, H, F, E, topk, training=True, seed=0):
+def _mk_layer(rt, T, H, F, E, topk, training=True, seed=0, tn_gemm=True):
     from roc_shmem_b200.ops.moe import MoELayer, interleave_gate_up
     torch.manual_seed(seed)
-    layer = MoELayer(rt, H, F, E, topk, T, capacity_factor=2.0, training=training)
+    layer = MoELayer(rt, H, F, E, topk, T, capacity_factor=2.0, training=training, tn_gemm=tn_gemm)
     w1 = (torch.randn(E, F, H, device="cuda") * 0.05).to(torch.bfloat16)
     w3 = (torch.randn(E, F, H, device="cuda") * 0.05).to(torch.bfloat16)
     w2 = (torch.randn(E, H, F, device="cuda") * 0.05).to(torch.bfloat16)
@@ -71,6 +71,33 @@ def test_grouped_gemm_dynamic_rows_and_gated_epilogue(rt):
         assert (c[g * M:(g + 1) * M].float() - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-2
 
 
+def test_grouped_gemm_transposed_operands(rt):
+    """C_g = A_g^T · B_g on token-major operands (MN-major tensor-core descriptors), ragged token counts."""
+    from roc_shmem_b200.ops.moe import grouped_gemm_tn, zero_pad_rows
+    torch.manual_seed(3)
+    G, cap, M, N = 4, 768, 512, 256
+    a = torch.randn(G * cap, M, device="cuda").to(torch.bfloat16)
+    b = torch.randn(G * cap, N, device="cuda").to(torch.bfloat16)
+    a[5, 7] = float("nan")                                   # stale garbage beyond the count must not leak in ...
+    counts = torch.tensor([768, 1, 0, 333], dtype=torch.int32, device="cuda")
+    a[cap + 70, 3] = float("inf")                            # ... nor from rows beyond the padded 64-row block
+    a[5, 7] = 1.0
+    zero_pad_rows(a, G, counts)
+    zero_pad_rows(b, G, counts)
+    assert a[cap + 1:cap + 64].abs().max().item() == 0 and a[cap, 0].item() != 0 and a[cap + 64].abs().max().item() != 0
+    c = torch.full((G * M, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        grouped_gemm_tn(a, b, c, G, counts)
+    torch.cuda.synchronize()
+    from roc_shmem_b200.ops.moe import moe_lib
+    assert moe_lib().bshmem_moe_gemm_error_site(1) == 0
+    for g, n in enumerate(counts.tolist()):
+        ref = a[g * cap:g * cap + n].float().t() @ b[g * cap:g * cap + n].float()
+        got = c[g * M:(g + 1) * M].float()
+        assert torch.isfinite(got).all(), g
+        assert (got - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2, g
+
+
 def test_router_matches_reference(rt):
     from roc_shmem_b200.baseline.moe import route
     from roc_shmem_b200.ops.moe import moe_lib
@@ -89,11 +116,11 @@ def test_router_matches_reference(rt):
     assert torch.allclose(w.view(T, topk)[same], rw[same], atol=2e-3)
 
 
-@pytest.mark.parametrize("training", [True, False])
-def test_moe_forward_backward_single_pe(rt, training):
+@pytest.mark.parametrize("training,tn_gemm", [(True, True), (True, False), (False, True)])
+def test_moe_forward_backward_single_pe(rt, training, tn_gemm):
     from roc_shmem_b200.baseline.moe import moe_reference_single
     T, H, F, E, topk = 768, 256, 512, 8, 2
-    layer, wr, w1, w3, w2 = _mk_layer(rt, T, H, F, E, topk, training=training)
+    layer, wr, w1, w3, w2 = _mk_layer(rt, T, H, F, E, topk, training=training, tn_gemm=tn_gemm)
     x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
     for _ in range(2):                                     # two calls: parity buffers, zeroed arrival words
         y = layer.forward(x)
