@@ -48,6 +48,8 @@ def main() -> None:
     rank, P = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
+    for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533")):
+        os.environ.setdefault(k, v)                        # plain `python -m ...` = one rank
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     E, topk = 8, 2
     if args.small:

@@ -137,11 +137,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) grouped_gemm_tn_kernel(const _
   gemm_mainloop<GroupedTN>(prm, smem_raw);
 }
 
-// Zero the token rows [count_g, next multiple of 64) of every group of a [G][cap][cols] bf16 buffer.
+// Zero the token rows [count_g, next multiple of 64) — rows [0, 64) of an empty group — of every group of a
+// [G][cap][cols] bf16 buffer.
 __global__ void zero_pad_rows_kernel(__nv_bfloat16* buf, const int* counts, int cap, int cols) {
   const int g = blockIdx.y;
   const int c = counts[g];
-  int end = (c + 63) / 64 * 64;
+  int end = c == 0 ? 64 : (c + 63) / 64 * 64;      // an empty group still feeds one (all-zero) block to the GEMM
   if (end > cap) end = cap;
   const int vec_per_row = cols / 8;
   const long long n = (long long)(end - c) * vec_per_row;
