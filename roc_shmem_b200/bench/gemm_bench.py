@@ -41,14 +41,50 @@ def time_fn(fn, iters: int, flush: torch.Tensor | None) -> float:
     return total / iters
 
 
+def run_fp8(args, dev) -> None:
+    from ..ops.gemm_fp8 import fp8_error_site, gemm_fp8, quantize_act, quantize_weight
+    if args.small:
+        M, N, K = 2048, 2048, 2048
+        qa = quantize_act(torch.randn(M, K, device=dev).to(torch.bfloat16))
+        qw = quantize_weight((torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16))
+        gemm_fp8(qa, qw)
+        torch.cuda.synchronize()
+        print(json.dumps({"small_fp8": [M, N, K], "error_site": fp8_error_site()}))
+        return
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for name, M, N, K in SHAPES:
+        a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+        qa, qw = quantize_act(a), quantize_weight(b)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ref = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ms_fp8 = time_fn(lambda: gemm_fp8(qa, qw, out, max_ctas=args.max_ctas), args.iters, flush)
+        ms_quant = time_fn(lambda: quantize_act(a), args.iters, flush)
+        ms_bf16 = time_fn(lambda: gemm_bf16(a, b, ref), args.iters, flush)
+        exact = qa.dequantize() @ qw.dequantize().t()
+        fl = 2.0 * M * N * K
+        row = {"shape": name, "M": M, "N": N, "K": K, "ms_fp8": round(ms_fp8, 4), "ms_quant_act": round(ms_quant, 4),
+               "ms_bf16_ours": round(ms_bf16, 4), "tflops_fp8": round(fl / ms_fp8 / 1e9, 1),
+               "fp8_over_bf16": round(ms_bf16 / ms_fp8, 3),
+               "max_abs_diff_vs_dequant_fp32": (out.float() - exact).abs().max().item(),
+               "max_abs_diff_vs_bf16": (out.float() - ref.float()).abs().max().item(), "ref_scale": ref.float().abs().max().item(),
+               "error_site": fp8_error_site()}
+        print(json.dumps(row), flush=True)
+        del a, b, qa, qw, out, ref, exact
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--mid", action="store_true", help="one launch of a 4-wave problem (592 tiles) for profiler captures")
     ap.add_argument("--max-ctas", type=int, default=0)
+    ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 kernel against the bf16 kernel and cuBLAS bf16")
     args = ap.parse_args()
     dev = torch.device("cuda")
+    if args.fp8:
+        run_fp8(args, dev)
+        return
     if args.small or args.mid:
         M, N, K = (4096, 9472, 4096) if args.mid else (2048, 2048, 2048)
         a = torch.randn(M, K, device=dev).to(torch.bfloat16)

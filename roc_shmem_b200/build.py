@@ -54,13 +54,32 @@ def _nvcc() -> str | None:
     return cand if Path(cand).exists() else None
 
 
+_INCLUDE_DIRS = [CSRC / "include", CSRC / "cuda", CSRC / "host"]
+
+
+def _includes(src: Path, seen: set[Path]) -> None:
+    """Transitive closure of the quoted #include files of `src` that live in this tree."""
+    if src in seen or not src.exists():
+        return
+    seen.add(src)
+    for line in src.read_text(errors="ignore").splitlines():
+        line = line.strip()
+        if line.startswith("#include \""):
+            name = line.split("\"")[1]
+            for d in [src.parent] + _INCLUDE_DIRS:
+                if (d / name).exists():
+                    _includes((d / name).resolve(), seen)
+                    break
+
+
 def _stale(out: Path, srcs: list[Path]) -> bool:
     if not out.exists():
         return True
     t = out.stat().st_mtime
-    deps = list(srcs) + list((CSRC / "include").glob("*")) + list((CSRC / "host").glob("*.h")) + \
-        list((CSRC / "cuda").glob("*.cuh"))
-    return any(d.exists() and d.stat().st_mtime > t for d in deps)
+    deps: set[Path] = set()
+    for s in srcs:
+        _includes(s.resolve(), deps)
+    return any(d.stat().st_mtime > t for d in deps)
 
 
 def _run(cmd: list[str], log: Path) -> None:
@@ -81,7 +100,16 @@ def build_host(force: bool = False) -> Path:
     return out
 
 
+def _compile_object(nvcc: str, src: Path, obj: Path, extra: list[str], force: bool) -> str:
+    if force or _stale(obj, [src]):
+        flags = [f for f in NVCC_FLAGS if f != "-shared"]
+        cmd = [nvcc] + NVCC_ARCH + flags + extra + ["-I", str(CSRC / "include"), "-I", str(CSRC / "cuda"), "-c", "-o", str(obj), str(src)]
+        _run(cmd, obj.with_suffix(".log"))       # .cc files are compiled as host C++ by nvcc
+    return obj.with_suffix(".log").read_text() if obj.with_suffix(".log").exists() else ""
+
+
 def build_cuda_target(name: str, force: bool = False) -> Path | None:
+    """One shared object per target; its sources are compiled to objects in parallel, then linked."""
     nvcc = _nvcc()
     if nvcc is None:
         return None
@@ -93,10 +121,14 @@ def build_cuda_target(name: str, force: bool = False) -> Path | None:
     srcs = [s for s in srcs if s.exists()]
     out = LIB / name
     if force or _stale(out, srcs):
-        cmd = [nvcc] + NVCC_ARCH + NVCC_FLAGS + extra + ["-I", str(CSRC / "include"), "-I", str(CSRC / "cuda"),
-                                                         "-o", str(out)] + [str(s) for s in srcs] + ["-lpthread", "-lrt", "-ldl"]
-        # .cc files listed next to .cu ones are compiled as host C++ by nvcc.
-        _run(cmd, LIB / (name + ".build.log"))
+        objdir = LIB / "obj" / name.replace(".so", "")
+        objdir.mkdir(parents=True, exist_ok=True)
+        objs = [objdir / (s.stem + ".o") for s in srcs]
+        with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 2)) as ex:
+            logs = list(ex.map(lambda so: _compile_object(nvcc, so[0], so[1], extra, force), zip(srcs, objs)))
+        cmd = [nvcc] + NVCC_ARCH + ["-shared", "-o", str(out)] + [str(o) for o in objs] + ["-lpthread", "-lrt", "-ldl"]
+        _run(cmd, LIB / (name + ".link.log"))
+        (LIB / (name + ".build.log")).write_text("\n".join(logs))     # registers / spills / shared memory per kernel
     return out
 
 

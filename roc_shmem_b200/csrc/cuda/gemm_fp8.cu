@@ -1,0 +1,386 @@
+// gemm_fp8.cu — block-scaled fp8 (e4m3) tcgen05 GEMM for sm_100a:
+//
+//   C[M,N] (bf16) = sum over 128-wide k-blocks kb of
+//                   sa[kb][m] * sb[kb][n/128] * ( A8[m, kb] · B8[n, kb]^T )
+//
+// A8: [M, K] e4m3 activations with one fp32 scale per row and 128 columns ("1x128"), stored
+// k-block-major (sa[kb * M + m]) so that the 32 rows of a warp read 128 contiguous bytes;
+// B8: [N, K] e4m3 weights with one fp32 scale per 128x128 block (sb[kb * (N/128) + n/128]).
+//
+// The scales differ from k-block to k-block, so the tensor core cannot keep one running
+// accumulator.  Each k-block's product (M128 x N256 x K128, four tcgen05.mma kind::f8f6f4)
+// goes into one of two 256-column TMEM buffers; sixteen epilogue warps read the buffer that
+// just completed, multiply by the row's scale and add into fp32 registers (64 per thread,
+// packed two-wide FMAs) while the tensor core fills the other buffer.  Four warps per SM
+// sub-partition hide the TMEM load latency.  One CTA per SM, persistent over 128x256 tiles:
+//   warp 0      TMA producer: 3-stage ring of 48 KiB (A 128 rows + B 256 rows of 128 bytes)
+//   warp 1      MMA issuer, commits each k-block to the stage's and the buffer's mbarrier
+//   warps 2-17  promote partial products (32 rows x 64 columns each), then convert, stage in
+//               swizzled smem and TMA-store
+// Every wait is bounded (see gemm_core.cuh); there is no counterpart in the reference.
+#include <cuda_fp8.h>
+
+#include "gemm_core.cuh"
+#include "tma_host.h"
+
+using namespace bshmem;
+using namespace bshmem::gemm;
+
+namespace {
+
+constexpr int FBM = 128, FBN = 256, FBK = 128;          // tile and k-block in elements (= bytes)
+constexpr int FSTAGES = 3;
+constexpr int FEPI_WARPS = 16;
+constexpr int FNUM_THREADS = 32 * (2 + FEPI_WARPS);
+constexpr uint32_t FA_BYTES = FBM * FBK, FB_BYTES = FBN * FBK, FSTAGE_BYTES = FA_BYTES + FB_BYTES;
+constexpr uint32_t FEPI_BYTES = 32 * 128;               // one warp: 32 rows x 64 bf16
+constexpr uint32_t FSMEM_TILES = FSTAGES * FSTAGE_BYTES + FEPI_WARPS * FEPI_BYTES;
+constexpr uint32_t FSMEM_BYTES = FSMEM_TILES + 256 + 1024;
+constexpr uint32_t kIdescFp8 = ptx::umma_idesc(0, 0, 128, 256);   // e4m3 x e4m3 -> fp32, M128 N256
+
+enum : int { ERR_F8_PART_FULL = 121, ERR_F8_PART_EMPTY = 122 };
+
+struct Fp8Params {
+  CoreParams core;             // num_m_blocks counts 128-row blocks
+  CUtensorMap map_a, map_b, map_c;
+  const float* sa;             // [K/128][M]
+  const float* sb;             // [K/128][N/128]
+};
+
+struct FSmem {
+  uint32_t base;
+  uint8_t* gen;
+  __device__ __forceinline__ uint32_t a(int s) const { return base + s * FSTAGE_BYTES; }
+  __device__ __forceinline__ uint32_t b(int s) const { return base + s * FSTAGE_BYTES + FA_BYTES; }
+  __device__ __forceinline__ uint32_t epi(int w) const { return base + FSTAGES * FSTAGE_BYTES + w * FEPI_BYTES; }
+  __device__ __forceinline__ uint32_t bars() const { return base + FSMEM_TILES; }
+  __device__ __forceinline__ uint32_t full(int s) const { return bars() + 8 * s; }
+  __device__ __forceinline__ uint32_t empty(int s) const { return bars() + 8 * (FSTAGES + s); }
+  __device__ __forceinline__ uint32_t part_full(int b) const { return bars() + 8 * (2 * FSTAGES + b); }
+  __device__ __forceinline__ uint32_t part_empty(int b) const { return bars() + 8 * (2 * FSTAGES + 2 + b); }
+  __device__ __forceinline__ uint32_t tmem_slot() const { return bars() + 8 * (2 * FSTAGES + 4); }
+  __device__ __forceinline__ volatile int* abort_flag() const {
+    return reinterpret_cast<volatile int*>(gen + FSMEM_TILES + 8 * (2 * FSTAGES + 4) + 8);
+  }
+};
+
+__global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(const __grid_constant__ Fp8Params prm) {
+  extern __shared__ uint8_t smem_raw[];
+  FSmem L;
+  {
+    uint32_t r = ptx::smem_u32(smem_raw);
+    L.base = (r + 1023u) & ~1023u;
+    L.gen = smem_raw + (L.base - r);
+  }
+  const CoreParams& cp = prm.core;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = cp.num_m_blocks * cp.num_n_blocks;
+  const int num_kb = cp.K / FBK;
+  Guard g{cp.err, L.abort_flag(), cp.timeout_ns};
+
+  if (threadIdx.x == 0) {
+    *L.abort_flag() = 0;
+    for (int s = 0; s < FSTAGES; ++s) { ptx::mbar_init(L.full(s), 1); ptx::mbar_init(L.empty(s), 1); }
+    for (int b = 0; b < 2; ++b) { ptx::mbar_init(L.part_full(b), 1); ptx::mbar_init(L.part_empty(b), FEPI_WARPS); }
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&prm.map_a);
+    ptx::prefetch_tensormap(&prm.map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(L.tmem_slot(), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(L.tmem_slot()));
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_blk, n_blk;
+        raster_coords(cp, tile, &m_blk, &n_blk);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(L.empty(s), ph ^ 1, g, ERR_PRODUCER_EMPTY)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(L.full(s), FSTAGE_BYTES);
+          ptx::tma_load_2d(L.a(s), &prm.map_a, L.full(s), kb * FBK, m_blk * FBM);
+          ptx::tma_load_2d(L.b(s), &prm.map_b, L.full(s), kb * FBK, n_blk * FBN);
+          if (++s == FSTAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      uint32_t it = 0;                       // k-blocks issued so far: buffer = it & 1, use count = it >> 1
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int buf = it & 1;
+          // the epilogue must have drained this buffer's previous product
+          if (!mbar_wait(L.part_empty(buf), ((it >> 1) & 1) ^ 1, g, ERR_F8_PART_EMPTY)) { ok = false; break; }
+          if (!mbar_wait(L.full(s), ph, g, ERR_MMA_FULL)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a0 = L.a(s), b0 = L.b(s);
+#pragma unroll
+          for (int k = 0; k < FBK / UMMA_K_BYTES; ++k)
+            ptx::umma_f8f6f4(tmem_base + buf * FBN, ptx::umma_desc_sw128(a0 + k * UMMA_K_BYTES),
+                             ptx::umma_desc_sw128(b0 + k * UMMA_K_BYTES), kIdescFp8, k != 0 ? 1u : 0u);
+          ptx::umma_commit(L.empty(s));            // smem stage reusable once these MMAs retire
+          ptx::umma_commit(L.part_full(buf));      // product of this k-block complete
+          if (++s == FSTAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------ promotion + epilogue -------------------------
+    const int ew = warp - 2;               // 0..15
+    const int quarter = warp & 3;          // TMEM lanes 32*quarter.. belong to this warp
+    const int cg = ew >> 2;                // columns [64*cg, 64*cg + 64) of the tile
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int m_blk, n_blk;
+      raster_coords(cp, tile, &m_blk, &n_blk);
+      const int row = m_blk * FBM + quarter * 32 + lane;
+      const float* sa = prm.sa + row;
+      const float* sb = prm.sb + (n_blk * (FBN / 128) + (cg >> 1));
+      const int sb_stride = cp.N / 128;
+      float2 acc[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.f, 0.f);
+      // scales are fetched three k-blocks ahead of their use (an L2 round trip is longer than a k-block)
+      auto scale_at = [&](int kb) -> float {
+        return kb < num_kb ? __ldg(sa + (size_t)kb * cp.M) * __ldg(sb + (size_t)kb * sb_stride) : 0.f;
+      };
+      float s0 = scale_at(0), s1 = scale_at(1), s2n = scale_at(2);
+#pragma unroll 1
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const float s3 = scale_at(kb + 3);
+        const int buf = it & 1;
+        if (!mbar_wait(L.part_full(buf), (it >> 1) & 1, g, ERR_F8_PART_FULL)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * FBN + cg * 64;
+        const float2 sc = make_float2(s0, s0);
+#ifndef BSHMEM_FP8_DIAG_NO_PROMOTE      // diagnostic build: tensor-core + TMA pipeline alone (wrong results)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[16];
+          ptx::tmem_ld_32x32b_x16(taddr + c * 16, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            acc[c * 8 + i] = __ffma2_rn(sc, make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), acc[c * 8 + i]);
+        }
+#else
+        acc[0].x += sc.x + __uint_as_float(taddr);
+#endif
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(L.part_empty(buf));
+        s0 = s1; s1 = s2n; s2n = s3;
+      }
+      if (!ok) break;
+      // ---- tile output: one 64-column chunk per warp through its swizzled staging buffer ----
+      if (lane == 0) ptx::tma_wait_group_read<0>();
+      __syncwarp();
+      const uint32_t rowbase = L.epi(ew) + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2* src = &acc[j * 4];
+        uint32_t w0 = pack_bf16(src[0].x, src[0].y), w1 = pack_bf16(src[1].x, src[1].y);
+        uint32_t w2 = pack_bf16(src[2].x, src[2].y), w3 = pack_bf16(src[3].x, src[3].y);
+        uint32_t dst = rowbase + ((j ^ (lane & 7)) << 4);
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::tma_store_2d(&prm.map_c, L.epi(ew), n_blk * FBN + cg * 64, m_blk * FBM + quarter * 32);
+        ptx::tma_commit_group();
+      }
+    }
+    if (lane == 0) ptx::tma_wait_group<0>();
+    __syncwarp();
+  }
+
+  // ------------------------------ teardown ---------------------------------------
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*L.abort_flag()) {
+    // let copies and MMAs that are still in flight land before smem/TMEM go away
+    unsigned long long t0 = ptx::globaltimer();
+    while (ptx::globaltimer() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- quantisers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint8_t to_e4m3(float x) {
+  return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+
+// Activations: one scale per row and 128 columns.  One warp per (row, k-block); lane l owns 4 elements.
+// q: [M, K] e4m3, scales: [K/128][M] fp32 with  x ≈ q * scale,  scale = absmax / 448 (1 if the block is all zero).
+__global__ void quant_act_1x128_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int ldx, uint8_t* __restrict__ q,
+                                       float* __restrict__ scales) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long nblk = (long long)M * (K / 128);
+  for (long long w = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); w < nblk; w += (long long)gridDim.x * warps_per_block) {
+    const int kb = (int)(w % (K / 128));
+    const int m = (int)(w / (K / 128));
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + (size_t)m * ldx + kb * 128 + lane * 4);
+    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    float v[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax > 0.f ? amax / 448.f : 1.f;
+    const float inv = 1.f / scale;
+    uint32_t packed = to_e4m3(v[0] * inv) | (to_e4m3(v[1] * inv) << 8) | (to_e4m3(v[2] * inv) << 16) | ((uint32_t)to_e4m3(v[3] * inv) << 24);
+    *reinterpret_cast<uint32_t*>(q + (size_t)m * K + kb * 128 + lane * 4) = packed;
+    if (lane == 0) scales[(size_t)kb * M + m] = scale;
+  }
+}
+
+// Weights: one scale per 128x128 block.  One CTA (256 threads) per block; scales: [K/128][N/128].
+__global__ void quant_w_128x128_kernel(const __nv_bfloat16* __restrict__ w, int N, int K, int ldw, uint8_t* __restrict__ q,
+                                       float* __restrict__ scales) {
+  __shared__ float red[8];
+  __shared__ float s_scale;
+  const int kb = blockIdx.x, nb = blockIdx.y;
+  const int t = threadIdx.x;
+  // thread t: row (t >> 1) + 0 of the block ... 64 elements of one row: rows = 128, two threads per row
+  const int r = t >> 1, c0 = (t & 1) * 64;
+  const __nv_bfloat16* src = w + (size_t)(nb * 128 + r) * ldw + kb * 128 + c0;
+  float v[64];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[i * 8 + 2 * j] = __low2float(p[j]);
+      v[i * 8 + 2 * j + 1] = __high2float(p[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(v[i * 8 + 2 * j]), fabsf(v[i * 8 + 2 * j + 1])));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((t & 31) == 0) red[t >> 5] = amax;
+  __syncthreads();
+  if (t == 0) {
+    float a = red[0];
+    for (int i = 1; i < 8; ++i) a = fmaxf(a, red[i]);
+    s_scale = a > 0.f ? a / 448.f : 1.f;
+    scales[(size_t)kb * (N / 128) + nb] = s_scale;
+  }
+  __syncthreads();
+  const float inv = 1.f / s_scale;
+  uint8_t* dst = q + (size_t)(nb * 128 + r) * K + kb * 128 + c0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float* e = &v[i * 16 + j * 4];
+      o[j] = to_e4m3(e[0] * inv) | (to_e4m3(e[1] * inv) << 8) | (to_e4m3(e[2] * inv) << 16) | ((uint32_t)to_e4m3(e[3] * inv) << 24);
+    }
+    reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+int* g_err_dev[64] = {};
+int g_sms[64] = {};
+
+int ensure(int dev) {
+  if (g_err_dev[dev]) return 0;
+  BSHMEM_CUDA_TRY(cudaMalloc(&g_err_dev[dev], sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaMemset(g_err_dev[dev], 0, sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(gemm_fp8_blockscale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FSMEM_BYTES));
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* bshmem_fp8_last_error() { return host::last_error().c_str(); }
+
+// C[M,N] bf16 = block-scaled A8[M,K] · B8[N,K]^T.  M % 128 == 0, N % 256 == 0, K % 128 == 0; A8/B8 dense
+// (row pitch K bytes), scale_a: [K/128][M], scale_b: [K/128][N/128], ldc in elements (% 8 == 0).
+int bshmem_gemm_fp8_blockscale(const void* A8, const float* scale_a, const void* B8, const float* scale_b, void* C, int M, int N,
+                               int K, int ldc, void* stream, int max_ctas, int timeout_ms) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % FBM || N % FBN || K % FBK || ldc % 8) {
+    host::last_error() = "fp8 gemm: needs M % 128 == 0, N % 256 == 0, K % 128 == 0, ldc % 8 == 0";
+    return 1;
+  }
+  int dev = 0;
+  BSHMEM_CUDA_TRY(cudaGetDevice(&dev));
+  int rc = ensure(dev);
+  if (rc) return rc;
+  Fp8Params p;
+  memset(&p, 0, sizeof(p));
+  p.core.M = M; p.core.N = N; p.core.K = K;
+  p.core.num_m_blocks = M / FBM; p.core.num_n_blocks = N / FBN;
+  p.core.group_m = 32;
+  p.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 4000) * 1000000ull;
+  p.core.err = g_err_dev[dev];
+  p.sa = scale_a; p.sb = scale_b;
+  rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A8, M, K, K, FBM, FBK);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B8, N, K, K, FBN, FBK);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&p.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, M, N, ldc, 32, 64);
+  if (rc) return rc;
+  int ctas = g_sms[dev];
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  const int tiles = p.core.num_m_blocks * p.core.num_n_blocks;
+  if (ctas > tiles) ctas = tiles;
+  gemm_fp8_blockscale_kernel<<<ctas, FNUM_THREADS, FSMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// x: [M, K] bf16 (ldx elements, % 4 == 0, 8-byte aligned rows) -> q [M, K] e4m3 + scales [K/128][M].
+int bshmem_fp8_quant_act(const void* x, int M, int K, int ldx, void* q, float* scales, void* stream) {
+  if (K % 128 || ldx % 4) { host::last_error() = "fp8 quant: K % 128 != 0 or ldx % 4 != 0"; return 1; }
+  long long nblk = (long long)M * (K / 128);
+  int blocks = (int)((nblk + 7) / 8 < 148 * 16 ? (nblk + 7) / 8 : 148 * 16);
+  if (blocks < 1) blocks = 1;
+  quant_act_1x128_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x), M, K, ldx,
+                                                                                static_cast<uint8_t*>(q), scales);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// w: [N, K] bf16 (ldw % 8 == 0) -> q [N, K] e4m3 + scales [K/128][N/128].
+int bshmem_fp8_quant_weight(const void* w, int N, int K, int ldw, void* q, float* scales, void* stream) {
+  if (K % 128 || N % 128 || ldw % 8) { host::last_error() = "fp8 quant: N, K % 128 != 0 or ldw % 8 != 0"; return 1; }
+  quant_w_128x128_kernel<<<dim3(K / 128, N / 128), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(w), N, K, ldw, static_cast<uint8_t*>(q), scales);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int bshmem_fp8_error_site(int clear) {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || !g_err_dev[dev]) return 0;
+  cudaMemcpy(&v, g_err_dev[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (clear && v) cudaMemset(g_err_dev[dev], 0, sizeof(int));
+  return v;
+}
+
+}  // extern "C"

@@ -153,6 +153,50 @@ template <typename T> union Vec16 {
   T e[16 / sizeof(T)];
 };
 
+// 16-byte vectors [v0, v1) of the reduction, striped over the block.  NS bounds the member count at compile
+// time, U vectors per thread are in flight together: all U x nsrc loads are issued before the first use.
+template <typename T, int OP, int NS, int U>
+__device__ __forceinline__ void reduce_vec_body(int nsrc, const T* const* srcs, int ndst, T* const* dsts, size_t v0, size_t v1) {
+  using A = typename Acc<T>::type;
+  constexpr int VE = 16 / sizeof(T);
+  const size_t tid = threadIdx.x, nth = blockDim.x;
+  const uint4* sp[NS];
+#pragma unroll
+  for (int k = 0; k < NS; ++k) sp[k] = reinterpret_cast<const uint4*>(srcs[k < nsrc ? k : 0]);
+  for (size_t base = v0; base < v1; base += (size_t)U * nth) {
+    Vec16<T> in[U][NS];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = base + u * nth + tid;
+      if (v < v1) {
+#pragma unroll
+        for (int k = 0; k < NS; ++k)
+          if (k < nsrc) in[u][k].raw = sp[k][v];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = base + u * nth + tid;
+      if (v < v1) {
+        A acc[VE];
+#pragma unroll
+        for (int e = 0; e < VE; ++e) acc[e] = to_acc<T>(in[u][0].e[e]);
+#pragma unroll
+        for (int k = 1; k < NS; ++k) {
+          if (k < nsrc) {
+#pragma unroll
+            for (int e = 0; e < VE; ++e) acc[e] = apply<A>(OP, acc[e], to_acc<T>(in[u][k].e[e]));
+          }
+        }
+        Vec16<T> out;
+#pragma unroll
+        for (int e = 0; e < VE; ++e) out.e[e] = from_acc<T>(acc[e]);
+        for (int d = 0; d < ndst; ++d) reinterpret_cast<uint4*>(dsts[d])[v] = out.raw;
+      }
+    }
+  }
+}
+
 // dst[i] = reduce over members k (in team order) of src_k[i], for i in [begin, end) elements;
 // the result goes to `ndst` destinations.  Vector body + scalar edges, striped over the block.
 template <typename T, int OP>
@@ -171,27 +215,12 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
     for (int k = 1; k < nsrc; ++k) acc = apply<A>(op, acc, to_acc<T>(srcs[k][i]));
     for (int d = 0; d < ndst; ++d) dsts[d][i] = from_acc<T>(acc);
   }
-  for (size_t v = vbeg / VE + tid; v < vend / VE; v += nth) {
-    // issue every member's load before the first use: up to 16 peer loads in flight per thread
-    Vec16<T> in[BSHMEM_MAX_PES];
-#pragma unroll
-    for (int k = 0; k < BSHMEM_MAX_PES; ++k)
-      if (k < nsrc) in[k].raw = reinterpret_cast<const uint4*>(srcs[k])[v];
-    A acc[VE];
-#pragma unroll
-    for (int e = 0; e < VE; ++e) acc[e] = to_acc<T>(in[0].e[e]);
-#pragma unroll
-    for (int k = 1; k < BSHMEM_MAX_PES; ++k) {
-      if (k < nsrc) {
-#pragma unroll
-        for (int e = 0; e < VE; ++e) acc[e] = apply<A>(op, acc[e], to_acc<T>(in[k].e[e]));
-      }
-    }
-    Vec16<T> out;
-#pragma unroll
-    for (int e = 0; e < VE; ++e) out.e[e] = from_acc<T>(acc[e]);
-    for (int d = 0; d < ndst; ++d) reinterpret_cast<uint4*>(dsts[d])[v] = out.raw;
-  }
+  // vector body: enough independent 16-byte loads per thread (members x unroll ~ 16) to cover the NVLink
+  // latency whatever the team size
+  const size_t v0 = vbeg / VE, v1 = vend / VE;
+  if (nsrc <= 4) reduce_vec_body<T, OP, 4, 4>(nsrc, srcs, ndst, dsts, v0, v1);
+  else if (nsrc <= 8) reduce_vec_body<T, OP, 8, 2>(nsrc, srcs, ndst, dsts, v0, v1);
+  else reduce_vec_body<T, OP, BSHMEM_MAX_PES, 1>(nsrc, srcs, ndst, dsts, v0, v1);
   size_t tail = (vend > begin) ? vend : begin;
   for (size_t i = tail + tid; i < end; i += nth) {
     A acc = to_acc<T>(srcs[0][i]);
@@ -201,8 +230,10 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
 }
 
 // Run-time operator -> compile-time instantiation (bitwise operators exist for integer types only).
+// Not inlined: one copy per element type is shared by every collective kernel of a translation unit,
+// which keeps the kernels (and their compile time) small; the call happens once per CTA and collective.
 template <typename T>
-__device__ __forceinline__ void reduce_range(int op, int nsrc, const T* const* srcs, int ndst, T* const* dsts,
+__device__ __noinline__ void reduce_range(int op, int nsrc, const T* const* srcs, int ndst, T* const* dsts,
                                              size_t begin, size_t end) {
   switch (op) {
     case BSHMEM_SUM: reduce_range_op<T, BSHMEM_SUM>(nsrc, srcs, ndst, dsts, begin, end); break;

@@ -168,7 +168,14 @@ __device__ __forceinline__ void copy_bytes(char* __restrict__ dst, const char* _
     const uint4* s4 = reinterpret_cast<const uint4*>(src + head);
     uint4* d4 = reinterpret_cast<uint4*>(dst + head);
     size_t i = r;
-    // four independent 16-byte accesses in flight per thread
+    // eight, then four independent 16-byte accesses in flight per thread
+    for (; i + 7 * (size_t)w < body; i += 8 * (size_t)w) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = s4[i + u * (size_t)w];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) d4[i + u * (size_t)w] = v[u];
+    }
     for (; i + 3 * (size_t)w < body; i += 4 * (size_t)w) {
       uint4 a = s4[i], b = s4[i + w], c = s4[i + 2 * (size_t)w], d = s4[i + 3 * (size_t)w];
       d4[i] = a; d4[i + w] = b; d4[i + 2 * (size_t)w] = c; d4[i + 3 * (size_t)w] = d;

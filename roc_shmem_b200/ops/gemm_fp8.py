@@ -1,0 +1,113 @@
+"""Block-scaled fp8 (e4m3) GEMM on the tcgen05 tensor cores, with its quantisers.
+
+Scaling follows the fine-grained recipe used for fp8 training: activations carry one fp32
+scale per row and 128 columns (stored ``[K/128, M]`` so a warp's rows are contiguous),
+weights one per 128x128 block (``[K/128, N/128]``).  The reference is a communication runtime
+and contains no GEMM, so there is no parity citation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import _native
+
+_declared = False
+
+
+def fp8_lib() -> C.CDLL:
+    global _declared
+    lib = _native.load("libbshmem_fp8.so")
+    if not _declared:
+        VP, I = C.c_void_p, C.c_int
+        lib.bshmem_fp8_last_error.restype = C.c_char_p
+        lib.bshmem_gemm_fp8_blockscale.restype = I
+        lib.bshmem_gemm_fp8_blockscale.argtypes = [VP, VP, VP, VP, VP, I, I, I, I, VP, I, I]
+        lib.bshmem_fp8_quant_act.restype = I
+        lib.bshmem_fp8_quant_act.argtypes = [VP, I, I, I, VP, VP, VP]
+        lib.bshmem_fp8_quant_weight.restype = I
+        lib.bshmem_fp8_quant_weight.argtypes = [VP, I, I, I, VP, VP, VP]
+        lib.bshmem_fp8_error_site.restype = I
+        lib.bshmem_fp8_error_site.argtypes = [I]
+        _declared = True
+    return lib
+
+
+@dataclass
+class Fp8Tensor:
+    """e4m3 payload ``q`` (uint8 view, [rows, K]) and its fp32 block scales."""
+    q: torch.Tensor
+    scales: torch.Tensor
+    kind: str               # "act" (1x128 blocks, scales [K/128, rows]) or "weight" (128x128, scales [K/128, rows/128])
+
+    def dequantize(self) -> torch.Tensor:
+        """fp32 reconstruction (for tests and reference computations)."""
+        rows, K = self.q.shape
+        x = self.q.view(torch.float8_e4m3fn).float().view(rows, K // 128, 128)
+        if self.kind == "act":
+            s = self.scales.t().contiguous().view(rows, K // 128, 1)
+        else:
+            s = self.scales.t().contiguous().repeat_interleave(128, dim=0).view(rows, K // 128, 1)
+        return (x * s).view(rows, K)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def quantize_act(x: torch.Tensor) -> Fp8Tensor:
+    """bf16 [M, K] (K % 128 == 0) → e4m3 with one scale per row and 128 columns."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] % 128:
+        raise ValueError("quantize_act needs a K-major bf16 matrix with K % 128 == 0")
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
+    s = torch.empty((K // 128, M), dtype=torch.float32, device=x.device)
+    lib = fp8_lib()
+    st = lib.bshmem_fp8_quant_act(x.data_ptr(), M, K, x.stride(0), q.data_ptr(), s.data_ptr(), _stream())
+    if st != 0:
+        raise RuntimeError(f"fp8 quantize_act failed ({st}): {lib.bshmem_fp8_last_error().decode()}")
+    return Fp8Tensor(q, s, "act")
+
+
+def quantize_weight(w: torch.Tensor) -> Fp8Tensor:
+    """bf16 [N, K] (N, K % 128 == 0) → e4m3 with one scale per 128x128 block."""
+    if w.dtype != torch.bfloat16 or w.dim() != 2 or w.stride(1) != 1 or w.shape[1] % 128 or w.shape[0] % 128:
+        raise ValueError("quantize_weight needs a K-major bf16 matrix with N % 128 == 0 and K % 128 == 0")
+    N, K = w.shape
+    q = torch.empty((N, K), dtype=torch.uint8, device=w.device)
+    s = torch.empty((K // 128, N // 128), dtype=torch.float32, device=w.device)
+    lib = fp8_lib()
+    st = lib.bshmem_fp8_quant_weight(w.data_ptr(), N, K, w.stride(0), q.data_ptr(), s.data_ptr(), _stream())
+    if st != 0:
+        raise RuntimeError(f"fp8 quantize_weight failed ({st}): {lib.bshmem_fp8_last_error().decode()}")
+    return Fp8Tensor(q, s, "weight")
+
+
+def gemm_fp8(a: Fp8Tensor, b: Fp8Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
+             timeout_ms: int = 2000) -> torch.Tensor:
+    """out[M, N] (bf16) = dequant(a)[M, K] @ dequant(b)[N, K].T, scales applied per 128-wide k-block
+    to fp32 partial products.  M % 128 == 0, N % 256 == 0, K % 128 == 0.  Current CUDA stream."""
+    if a.kind != "act" or b.kind != "weight":
+        raise ValueError("gemm_fp8 takes (activation, weight)")
+    M, K = a.q.shape
+    N = b.q.shape[0]
+    if b.q.shape[1] != K:
+        raise ValueError("K mismatch")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.q.device)
+    elif out.shape != (M, N) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ValueError("bad output tensor")
+    lib = fp8_lib()
+    st = lib.bshmem_gemm_fp8_blockscale(a.q.data_ptr(), a.scales.data_ptr(), b.q.data_ptr(), b.scales.data_ptr(), out.data_ptr(),
+                                        M, N, K, out.stride(0), _stream(), max_ctas, timeout_ms)
+    if st != 0:
+        raise RuntimeError(f"fp8 gemm failed ({st}): {lib.bshmem_fp8_last_error().decode()}")
+    return out
+
+
+def fp8_error_site(clear: bool = True) -> int:
+    """0 if no in-kernel bounded wait ran out since the last clear, else the site code."""
+    return int(fp8_lib().bshmem_fp8_error_site(int(clear)))
