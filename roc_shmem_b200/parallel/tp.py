@@ -32,11 +32,7 @@ class RowParallelLinear:
             raise ValueError("token count must divide by the number of PEs")
         dev = rt.device
         self.weight = torch.empty((self.N, self.K), dtype=dtype, device=dev)
-        # double-buffered device inputs + a copy stream: the host->device copy of step i+1 overlaps step i
-        self.x_bufs = [torch.empty((self.M, self.K), dtype=dtype, device=dev) for _ in range(2)]
-        self.copy_stream = torch.cuda.Stream(device=dev)
-        self.copied = [torch.cuda.Event() for _ in range(2)]
-        self.consumed = [torch.cuda.Event() for _ in range(2)]
+        self.x_bufs = None          # step_from_host() allocates its double-buffered inputs on first use
         self._step = 0
         self.metric_dev = torch.zeros(1, dtype=torch.float32, device=dev)
         self._launches = 0
@@ -50,19 +46,28 @@ class RowParallelLinear:
             self.out = self._fused.out
             self.algorithm = self._fused.algorithm
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, weight: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        w = self.weight if weight is None else weight
+        out = self.out if out is None else out
         if self._fused is None:
-            gemm_bf16(x, self.weight, self.out)
+            gemm_bf16(x, w, out)
             self._launches += 1
-            return self.out
-        self._launches += self._fused(x, self.weight)
-        return self.out
+            return out
+        self._launches += self._fused(x, w, out)
+        return out
 
     __call__ = forward
 
     def step_from_host(self, x_host: torch.Tensor, metric_host: torch.Tensor) -> None:
         """One serving-style step: pinned host activations -> device (copy stream, double-buffered so that
         the copy of the next step overlaps this step's kernel), the layer, one scalar of the result back."""
+        if self.x_bufs is None:
+            # double-buffered device inputs + a copy stream: the host->device copy of step i+1 overlaps step i
+            dev = self.rt.device
+            self.x_bufs = [torch.empty((self.M, self.K), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+            self.copy_stream = torch.cuda.Stream(device=dev)
+            self.copied = [torch.cuda.Event() for _ in range(2)]
+            self.consumed = [torch.cuda.Event() for _ in range(2)]
         i = self._step & 1
         main = torch.cuda.current_stream()
         with torch.cuda.stream(self.copy_stream):
@@ -79,6 +84,58 @@ class RowParallelLinear:
 
     def reset_launch_count(self) -> None:
         self._launches = 0
+
+    def launch_count(self) -> int:
+        return self._launches
+
+    def check(self) -> None:
+        site = gemm_error_site()
+        if site:
+            raise RuntimeError(f"a bounded in-kernel wait ran out (site {site})")
+        if self._fused is not None:
+            self._fused.check()
+
+
+class ColumnParallelLinear:
+    """x_shard: [M/P, K] (this rank's token rows) ; weight: [N/P, K] ; returns [M, N/P] =
+    all_gather_rows(x) @ w.T.  The caller writes its rows into ``self.x_shard`` (a view of the symmetric
+    gathered buffer) or passes them to forward(), which copies them there; after the call ``self.gathered``
+    holds all M rows (reused by the weight-gradient GEMM of a backward pass)."""
+
+    def __init__(self, rt, in_features: int, out_features_per_rank: int, max_tokens: int):
+        self.rt, self.P = rt, rt.n_pes
+        self.K, self.N, self.M = in_features, out_features_per_rank, max_tokens
+        if self.M % self.P:
+            raise ValueError("token count must divide by the number of PEs")
+        dev = rt.device
+        self.weight = torch.empty((self.N, self.K), dtype=torch.bfloat16, device=dev)
+        self._launches = 0
+        if self.P == 1:
+            self.gathered = torch.empty((self.M, self.K), dtype=torch.bfloat16, device=dev)
+            self.x_shard = self.gathered
+            self.out = torch.empty((self.M, self.N), dtype=torch.bfloat16, device=dev)
+            self._fused = None
+            self.algorithm = "tcgen05 GEMM; 1 PE: no collective"
+        else:
+            from ..ops.fused_tp import AllGatherGemm
+            self._fused = AllGatherGemm(rt, self.M, self.N, self.K)
+            self.gathered, self.x_shard, self.out = self._fused.xg, self._fused.x_shard, self._fused.out
+            self.algorithm = self._fused.algorithm
+
+    def forward(self, x_shard: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        w = self.weight if weight is None else weight
+        out = self.out if out is None else out
+        if x_shard is not None and x_shard.data_ptr() != self.x_shard.data_ptr():
+            self.x_shard.copy_(x_shard)
+        if self._fused is None:
+            gemm_bf16(self.gathered, w, out)
+            self._launches += 1
+        else:
+            self._launches += self._fused(w, out)
+        return out
+
+    __call__ = forward
 
     def launch_count(self) -> int:
         return self._launches

@@ -35,3 +35,10 @@ def test_rank_leaves_between_steps_peers_time_out():
     p = _torchrun(2, ["tests/mp/failure_worker.py"], 29612)
     assert p.returncode == 0, p.stdout[-4000:] + p.stderr[-4000:]
     assert "SURVIVOR_SAW_TIMEOUT" in p.stdout
+
+
+def test_model_blocks_two_pes():
+    _need(2)
+    p = _torchrun(2, ["tests/mp/models_worker.py"], 29613)
+    assert p.returncode == 0, p.stdout[-4000:] + p.stderr[-4000:]
+    assert p.stdout.count("MODELS_OK") == 2
