@@ -39,7 +39,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--out", default="")
-    ap.add_argument("--ctas", type=int, default=64)
+    ap.add_argument("--ctas", type=int, default=128)
     ap.add_argument("--nvls", action="store_true")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))

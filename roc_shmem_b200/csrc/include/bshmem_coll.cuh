@@ -218,7 +218,8 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
   // vector body: enough independent 16-byte loads per thread (members x unroll ~ 16) to cover the NVLink
   // latency whatever the team size
   const size_t v0 = vbeg / VE, v1 = vend / VE;
-  if (nsrc <= 4) reduce_vec_body<T, OP, 4, 4>(nsrc, srcs, ndst, dsts, v0, v1);
+  if (nsrc <= 2) reduce_vec_body<T, OP, 2, 8>(nsrc, srcs, ndst, dsts, v0, v1);
+  else if (nsrc <= 4) reduce_vec_body<T, OP, 4, 4>(nsrc, srcs, ndst, dsts, v0, v1);
   else if (nsrc <= 8) reduce_vec_body<T, OP, 8, 2>(nsrc, srcs, ndst, dsts, v0, v1);
   else reduce_vec_body<T, OP, BSHMEM_MAX_PES, 1>(nsrc, srcs, ndst, dsts, v0, v1);
   size_t tail = (vend > begin) ? vend : begin;
