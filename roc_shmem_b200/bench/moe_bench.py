@@ -40,6 +40,7 @@ def timed(fn, iters, rt):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--mid", action="store_true", help="4096 tokens, hidden 2048, ffn 4096 (profiler captures)")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--out", default="")
@@ -54,6 +55,8 @@ def main() -> None:
     E, topk = 8, 2
     if args.small:
         T, H, F = 1024, 512, 1024
+    elif args.mid:
+        T, H, F = 4096, 2048, 4096
     else:
         T, H, F = args.tokens, 4096, 14336
     G = E // P

@@ -43,11 +43,14 @@ def timed(fn, iters: int, rt) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--mid", action="store_true", help="4096-token, hidden 4096, ffn 4096*P problem (profiler captures)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default="")
     ap.add_argument("--peak-tflops", type=float, default=1399.1)
     ap.add_argument("--link-gbs", type=float, default=770.0)
     args = ap.parse_args()
+    for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29535")):
+        os.environ.setdefault(k, v)                        # plain `python -m ...` = one rank
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -57,6 +60,8 @@ def main() -> None:
     P = world
     if args.small:
         M, H, F = 512 * P, 512, 256 * P
+    elif args.mid:
+        M, H, F = 4096, 4096, 4096 * P
     else:
         M, H, F = 8192, 8192, 28672
     results = {"world": P, "M": M, "hidden": H, "ffn": F}

@@ -98,7 +98,7 @@ __global__ void k_signal(State s, int pe, uint64_t sig_off, uint64_t value, int 
 }
 
 // Device-initiated put / get of a large message striped over the grid (block scope per CTA).
-__global__ void k_rma(State s, int pe, uint64_t sym_off, char* local, uint64_t n, int is_put, int scope) {
+__global__ void __launch_bounds__(1024) k_rma(State s, int pe, uint64_t sym_off, char* local, uint64_t n, int is_put, int scope) {
   uint64_t per = ((n + gridDim.x - 1) / gridDim.x + 15) & ~15ull;
   uint64_t b = per * blockIdx.x, e = b + per < n ? b + per : n;
   if (b >= n) return;
@@ -617,8 +617,13 @@ int bshmem_gpu_rma_kernel(bshmem_handle_t h, void* sym, void* local, uint64_t n,
   if (!h->to_offset(sym, n, &off) || pe < 0 || pe >= g->n_pes()) return BSHMEM_ERR_RANGE;
   if (ctas < 1) ctas = 1;
   if (threads < 32) threads = 32;
+  if (threads > 1024) threads = 1024;
   k_rma<<<ctas, threads, 0, g->stream()>>>(g->state(), pe, off, static_cast<char*>(local), n, is_put, scope);
-  if (cudaGetLastError() != cudaSuccess) return BSHMEM_ERR_CUDA;
+  cudaError_t ce = cudaGetLastError();
+  if (ce != cudaSuccess) {
+    g_err = std::string("rma kernel launch: ") + cudaGetErrorString(ce);
+    return BSHMEM_ERR_CUDA;
+  }
   return BSHMEM_OK;
 }
 

@@ -218,10 +218,19 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
   // vector body: enough independent 16-byte loads per thread (members x unroll ~ 16) to cover the NVLink
   // latency whatever the team size
   const size_t v0 = vbeg / VE, v1 = vend / VE;
-  if (nsrc <= 2) reduce_vec_body<T, OP, 2, 8>(nsrc, srcs, ndst, dsts, v0, v1);
-  else if (nsrc <= 4) reduce_vec_body<T, OP, 4, 4>(nsrc, srcs, ndst, dsts, v0, v1);
-  else if (nsrc <= 8) reduce_vec_body<T, OP, 8, 2>(nsrc, srcs, ndst, dsts, v0, v1);
-  else reduce_vec_body<T, OP, BSHMEM_MAX_PES, 1>(nsrc, srcs, ndst, dsts, v0, v1);
+  // the unrolled variants exist for the element types and operators of bulk reductions (sum / max / min of
+  // float, double, half, bf16, int32, int64); everything else takes the generic body, which keeps the build short
+  constexpr bool kHot = (OP == BSHMEM_SUM || OP == BSHMEM_MAX || OP == BSHMEM_MIN) &&
+                        (std::is_same<T, float>::value || std::is_same<T, double>::value || std::is_same<T, __half>::value ||
+                         std::is_same<T, __nv_bfloat16>::value || std::is_same<T, int32_t>::value || std::is_same<T, long long>::value);
+  if constexpr (kHot) {
+    if (nsrc <= 2) reduce_vec_body<T, OP, 2, 8>(nsrc, srcs, ndst, dsts, v0, v1);
+    else if (nsrc <= 4) reduce_vec_body<T, OP, 4, 4>(nsrc, srcs, ndst, dsts, v0, v1);
+    else if (nsrc <= 8) reduce_vec_body<T, OP, 8, 2>(nsrc, srcs, ndst, dsts, v0, v1);
+    else reduce_vec_body<T, OP, BSHMEM_MAX_PES, 1>(nsrc, srcs, ndst, dsts, v0, v1);
+  } else {
+    reduce_vec_body<T, OP, BSHMEM_MAX_PES, 1>(nsrc, srcs, ndst, dsts, v0, v1);
+  }
   size_t tail = (vend > begin) ? vend : begin;
   for (size_t i = tail + tid; i < end; i += nth) {
     A acc = to_acc<T>(srcs[0][i]);

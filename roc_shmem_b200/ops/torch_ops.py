@@ -93,3 +93,121 @@ class Linear(torch.nn.Module):
         lead = x.shape[:-1]
         y = torch.ops.bshmem.linear(x.reshape(-1, x.shape[-1]), self.weight)
         return y.reshape(*lead, -1)
+
+
+# ---- collectives on the calling PE's runtime (roc_shmem_b200.current()) --------------------------------
+# Arbitrary tensors are staged through symmetric scratch that is cached per (shape, dtype); symmetric
+# tensors (rt.empty / rt.zeros) are used in place.  Works on the NVLink and on the CPU backend.
+_scratch: dict = {}
+
+
+def _sym(rt, key: str, shape, dtype) -> torch.Tensor:
+    k = (id(rt), key, tuple(shape), dtype)
+    t = _scratch.get(k)
+    if t is None:
+        t = rt.empty(tuple(shape), dtype)
+        _scratch[k] = t
+    return t
+
+
+def release_scratch() -> None:
+    """Free the cached symmetric staging buffers (collective: every PE must call it)."""
+    from .. import current
+    rt = current()
+    for k in [k for k in _scratch if k[0] == id(rt)]:
+        rt.free(_scratch.pop(k))
+
+
+@torch.library.custom_op("bshmem::all_reduce", mutates_args=())
+def all_reduce(x: torch.Tensor, op: str = "sum") -> torch.Tensor:
+    """Reduction over all PEs (`to_all`); every PE gets the result."""
+    from .. import current
+    rt = current()
+    src, dst = _sym(rt, "ar_src", x.shape, x.dtype), _sym(rt, "ar_dst", x.shape, x.dtype)
+    src.copy_(x)
+    rt.reduce(dst, src, op)
+    return dst.clone()
+
+
+@all_reduce.register_fake
+def _(x, op="sum"):
+    return torch.empty_like(x)
+
+
+@torch.library.custom_op("bshmem::all_gather", mutates_args=())
+def all_gather(x: torch.Tensor) -> torch.Tensor:
+    """Concatenation of every PE's `x` along dimension 0 (`fcollect`)."""
+    from .. import current
+    rt = current()
+    src = _sym(rt, "ag_src", x.shape, x.dtype)
+    dst = _sym(rt, "ag_dst", (rt.n_pes * x.shape[0],) + tuple(x.shape[1:]), x.dtype)
+    src.copy_(x)
+    rt.fcollect(dst, src)
+    return dst.clone()
+
+
+@all_gather.register_fake
+def _(x):
+    from .. import current
+    return x.new_empty((current().n_pes * x.shape[0],) + tuple(x.shape[1:]))
+
+
+@torch.library.custom_op("bshmem::reduce_scatter", mutates_args=())
+def reduce_scatter(x: torch.Tensor, op: str = "sum") -> torch.Tensor:
+    """This PE's 1/n slice (dimension 0) of the reduction of every PE's `x`."""
+    from .. import current
+    rt = current()
+    if x.shape[0] % rt.n_pes:
+        raise ValueError("reduce_scatter: dimension 0 must divide by the number of PEs")
+    src = _sym(rt, "rs_src", x.shape, x.dtype)
+    dst = _sym(rt, "rs_dst", (x.shape[0] // rt.n_pes,) + tuple(x.shape[1:]), x.dtype)
+    src.copy_(x)
+    rt.reduce_scatter(dst, src, op)
+    return dst.clone()
+
+
+@reduce_scatter.register_fake
+def _(x, op="sum"):
+    from .. import current
+    return x.new_empty((x.shape[0] // current().n_pes,) + tuple(x.shape[1:]))
+
+
+@torch.library.custom_op("bshmem::all_to_all", mutates_args=())
+def all_to_all(x: torch.Tensor) -> torch.Tensor:
+    """Block k (dimension 0 split in n equal blocks) of PE j's `x` becomes block j of PE k's result."""
+    from .. import current
+    rt = current()
+    if x.shape[0] % rt.n_pes:
+        raise ValueError("all_to_all: dimension 0 must divide by the number of PEs")
+    src, dst = _sym(rt, "a2a_src", x.shape, x.dtype), _sym(rt, "a2a_dst", x.shape, x.dtype)
+    src.copy_(x)
+    rt.alltoall(dst, src)
+    return dst.clone()
+
+
+@all_to_all.register_fake
+def _(x):
+    return torch.empty_like(x)
+
+
+def _ar_backward(ctx, g):
+    return torch.ops.bshmem.all_reduce(g.contiguous(), "sum"), None
+
+
+def _ag_backward(ctx, g):
+    return torch.ops.bshmem.reduce_scatter(g.contiguous(), "sum")
+
+
+def _rs_backward(ctx, g):
+    return torch.ops.bshmem.all_gather(g.contiguous()), None
+
+
+def _a2a_backward(ctx, g):
+    return torch.ops.bshmem.all_to_all(g.contiguous())
+
+
+# gradients of the sum-collectives are the matching collectives (valid for op == "sum")
+all_reduce.register_autograd(_ar_backward)
+all_gather.register_autograd(_ag_backward)
+reduce_scatter.register_autograd(_rs_backward)
+all_to_all.register_autograd(_a2a_backward)

@@ -212,3 +212,34 @@ def test_group_team_split_and_team_reduce(group):
     for _ in range(5):
         group.collective(gpu.COLL_REDUCE, dst, src, n, dtype=torch.float32, op=0, team_slot=slots[0], ctas=1)
     assert bool((dst[0] == 4).all())
+
+
+@pytest.mark.parametrize("scope", ["thread", "warp", "block"])
+@pytest.mark.parametrize("put", [True, False])
+def test_device_rma_matrix_sizes_and_alignments(rt, scope, put):
+    """The reference's functional sweep (clients/functional_tests/driver.sh:62-86: one work-group of 64 threads and
+    25 work-groups of 1024 threads, sizes in powers of two) plus odd sizes and misaligned ends, checked byte-exactly
+    with guard bytes on both sides."""
+    sym = rt.empty((1 << 20,), torch.uint8)
+    local = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
+    pattern = (torch.arange(1 << 20, device="cuda") * 7 + 3).to(torch.uint8)
+    for ctas, threads in ((1, 64), (25, 1024)):
+        for nbytes in (1, 2, 4, 8, 15, 16, 64, 100, 1024, 4097, 32768, 65536 + 5, (1 << 19) + 13):
+            for off_sym, off_loc in ((0, 0), (1, 1), (16, 3), (5, 64)):
+                if nbytes > 4096 and (off_sym, off_loc) == (16, 3) and scope == "thread":
+                    continue                                   # keep the byte-wise single-thread path short
+                s = sym[256 + off_sym:256 + off_sym + nbytes]
+                l = local[256 + off_loc:256 + off_loc + nbytes]
+                if put:
+                    sym.fill_(0xEE)
+                    local.copy_(pattern)
+                else:
+                    sym.copy_(pattern)
+                    local.fill_(0xEE)
+                rt.rma_kernel(s, l, 0, put=put, scope=scope, ctas=ctas, threads=threads, nbytes=nbytes)
+                rt.quiet()
+                dst, src, o_dst, o_src = (sym, pattern, off_sym, off_loc) if put else (local, pattern, off_loc, off_sym)
+                lo, hi = 256 + o_dst, 256 + o_dst + nbytes
+                assert torch.equal(dst[lo:hi], src[256 + o_src:256 + o_src + nbytes]), (scope, put, ctas, nbytes, off_sym, off_loc)
+                assert bool((dst[:lo] == 0xEE).all()) and bool((dst[hi:] == 0xEE).all()), "guard bytes touched"
+    rt.free(sym)
