@@ -140,7 +140,9 @@ __device__ int reduce_typed(const State& s, const DTeam& t, const CollArgs& a, i
   const T* src = reinterpret_cast<const T*>(s.heap_base[s.my_pe] + a.src_off);
   if (a.kind == BSHMEM_COLL_REDUCE_SCATTER) return coll::team_reduce_scatter<T>(s, t, a.op, d, src, a.n, cta, ncta);
   if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value) {
-    if (a.use_nvls && s.mc_base && a.op == BSHMEM_SUM && ((a.dst_off | a.src_off) & 15) == 0 && (a.n * sizeof(T)) % 16 == 0)
+    // the multicast mapping spans every PE, so the in-switch reduction only fits a team that is the whole world
+    if (a.use_nvls && s.mc_base && t.size == s.n_pes && a.op == BSHMEM_SUM && ((a.dst_off | a.src_off) & 15) == 0 &&
+        (a.n * sizeof(T)) % 16 == 0)
       return coll::team_reduce_nvls<T>(s, t, d, src, a.n, cta, ncta);
   }
   return coll::team_reduce<T>(s, t, a.op, d, src, a.n, cta, ncta);
