@@ -12,6 +12,7 @@
 // (library/src/host/host.cpp:160-235, host_templates.hpp) and the GPU-IB backend
 // wiring (gpu_ib/backend_ib.cpp:70-111); there is no NIC, so no queue pairs,
 // segments or doorbells exist here.
+#include <vector>
 #include <cuda_runtime.h>
 
 #include <cstring>
@@ -226,8 +227,9 @@ class GpuBackend final : public Backend {
     stream_ = own_stream_;
     RT_TRY(cudaHostAlloc(&pinned_, sizeof(Pinned), cudaHostAllocMapped));
     memset(pinned_, 0, sizeof(Pinned));
-    RT_TRY(cudaMalloc(&dstats_, sizeof(unsigned long long) * BSHMEM_DSTAT_COUNT));
-    RT_TRY(cudaMemset(dstats_, 0, sizeof(unsigned long long) * BSHMEM_DSTAT_COUNT));
+    // counters followed by the (initially disabled) event ring
+    RT_TRY(cudaMalloc(&dstats_, sizeof(unsigned long long) * (BSHMEM_DSTAT_COUNT + BSHMEM_TRACE_WORDS)));
+    RT_TRY(cudaMemset(dstats_, 0, sizeof(unsigned long long) * (BSHMEM_DSTAT_COUNT + BSHMEM_TRACE_WORDS)));
     RT_TRY(cudaMalloc(&dstatus_, sizeof(int)));
     RT_TRY(cudaMemset(dstatus_, 0, sizeof(int)));
     memset(&state_, 0, sizeof(state_));
@@ -600,6 +602,39 @@ int bshmem_gpu_get_device_stats(bshmem_handle_t h, uint64_t* out, int n) {
   unsigned long long tmp[BSHMEM_DSTAT_COUNT];
   if (cudaMemcpy(tmp, g->dstats(), sizeof(tmp), cudaMemcpyDeviceToHost) != cudaSuccess) return BSHMEM_ERR_CUDA;
   for (int i = 0; i < n && i < BSHMEM_DSTAT_COUNT; ++i) out[i] = tmp[i];
+  return BSHMEM_OK;
+}
+// Device timeline: keep the last `capacity` events (0 switches tracing off; at most BSHMEM_TRACE_MAX_EVENTS).
+// Synchronises the runtime's stream, so call it between kernels.
+int bshmem_gpu_trace_enable(bshmem_handle_t h, int capacity) {
+  GpuBackend* g = gpu_of(h);
+  if (!g || !g->dstats()) return BSHMEM_ERR_STATE;
+  if (capacity < 0 || capacity > BSHMEM_TRACE_MAX_EVENTS) return BSHMEM_ERR_INVALID;
+  if (cudaStreamSynchronize(g->stream()) != cudaSuccess) return BSHMEM_ERR_CUDA;
+  unsigned long long head[2] = {(unsigned long long)capacity, 0ull};
+  return cudaMemcpy(g->dstats() + BSHMEM_DSTAT_COUNT, head, sizeof(head), cudaMemcpyHostToDevice) == cudaSuccess ? BSHMEM_OK
+                                                                                                                  : BSHMEM_ERR_CUDA;
+}
+// Copies the recorded events, oldest first, into out[4 * max_events] (time ns, op | pe << 8 | block << 32, bytes,
+// sequence number); *n_out = events copied, *total = events recorded since tracing was enabled.
+int bshmem_gpu_trace_read(bshmem_handle_t h, uint64_t* out, int max_events, int* n_out, uint64_t* total) {
+  GpuBackend* g = gpu_of(h);
+  if (!g || !g->dstats() || !out || !n_out) return BSHMEM_ERR_STATE;
+  if (cudaStreamSynchronize(g->stream()) != cudaSuccess) return BSHMEM_ERR_CUDA;
+  std::vector<unsigned long long> buf(BSHMEM_TRACE_WORDS);
+  if (cudaMemcpy(buf.data(), g->dstats() + BSHMEM_DSTAT_COUNT, sizeof(unsigned long long) * BSHMEM_TRACE_WORDS,
+                 cudaMemcpyDeviceToHost) != cudaSuccess)
+    return BSHMEM_ERR_CUDA;
+  const unsigned long long cap = buf[0], count = buf[1];
+  if (total) *total = count;
+  unsigned long long have = cap ? (count < cap ? count : cap) : 0;
+  if (have > (unsigned long long)max_events) have = max_events;
+  for (unsigned long long k = 0; k < have; ++k) {
+    const unsigned long long seq = count - have + k;
+    const unsigned long long* e = &buf[2 + 4 * (seq % cap)];
+    for (int w = 0; w < 4; ++w) out[4 * k + w] = e[w];
+  }
+  *n_out = (int)have;
   return BSHMEM_OK;
 }
 int bshmem_gpu_reset_device_stats(bshmem_handle_t h) {

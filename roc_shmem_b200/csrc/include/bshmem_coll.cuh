@@ -101,7 +101,11 @@ __device__ __forceinline__ int team_sync(const State& s, const Team& t, int cta 
   __syncthreads();
   if (tid == 0) {
     *epoch_addr(s, t.slot, cta) = epoch;
-    if (s.stats) { dev::stat(s, BSHMEM_DSTAT_BARRIER); dev::stat(s, BSHMEM_DSTAT_BARRIER_NS, dev::timer() - t0); }
+    if (s.stats) {
+      dev::stat(s, BSHMEM_DSTAT_BARRIER);
+      dev::stat(s, BSHMEM_DSTAT_BARRIER_NS, dev::timer() - t0);
+      dev::trace(s, BSHMEM_TRACE_BARRIER, s.my_pe, dev::timer() - t0);
+    }
   }
   int rc = sync_status;
   __syncthreads();
@@ -296,7 +300,7 @@ __device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op
     split_range(se - sb, ncta, cta, VE, &b, &e);
     reduce_range<T>(op, t.size, srcs, t.size, dsts, sb + b, sb + e);
   }
-  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, 0); }
   return team_barrier(s, t, cta);         // results delivered; sources reusable
 }
 
@@ -313,7 +317,7 @@ __device__ __forceinline__ int team_reduce_scatter(const State& s, const Team& t
   T* mine[1] = {dest};
   // dest has its own offset; realign the vector path by handing in shifted bases
   reduce_range<T>(op, t.size, srcs, 1, mine, b, e);
-  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, 0); }
   return team_barrier(s, t, cta);
 }
 
@@ -328,7 +332,7 @@ __device__ __forceinline__ int team_broadcast(const State& s, const Team& t, voi
     const char* src = dev::ptr(s, reinterpret_cast<const char*>(source), dev::team_pe(t, root));
     dev::copy_bytes<dev::BLOCK>(reinterpret_cast<char*>(dest) + b, src + b, e - b);
   }
-  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, 0); }
   return team_barrier(s, t, cta);
 }
 
@@ -344,7 +348,7 @@ __device__ __forceinline__ int team_fcollect(const State& s, const Team& t, void
     char* d = dev::ptr(s, reinterpret_cast<char*>(dest), dev::team_pe(t, peer_idx)) + (size_t)t.my_idx * nbytes;
     dev::copy_bytes<dev::BLOCK>(d + b, reinterpret_cast<const char*>(source) + b, e - b);
   }
-  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, 0); }
   return team_barrier(s, t, cta);
 }
 
@@ -361,7 +365,7 @@ __device__ __forceinline__ int team_alltoall(const State& s, const Team& t, void
     const char* sp = reinterpret_cast<const char*>(source) + (size_t)j * nbytes;
     dev::copy_bytes<dev::BLOCK>(d + b, sp + b, e - b);
   }
-  if (cta == 0 && threadIdx.x == 0) dev::stat(s, BSHMEM_DSTAT_COLL);
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, 0); }
   return team_barrier(s, t, cta);
 }
 

@@ -65,6 +65,17 @@ enum {
   BSHMEM_DSTAT_PROXY_OPS, BSHMEM_DSTAT_COUNT
 };
 
+/* Optional event ring behind the counters (same allocation, so the state struct does not grow):
+ *   stats[BSHMEM_DSTAT_COUNT]      capacity in events, 0 = tracing off
+ *   stats[BSHMEM_DSTAT_COUNT + 1]  events recorded so far (the ring keeps the last `capacity`)
+ *   then 4 words per event: %globaltimer ns, op | pe << 8 | block << 32, bytes, sequence number */
+#define BSHMEM_TRACE_MAX_EVENTS 16384
+#define BSHMEM_TRACE_WORDS (2 + 4 * BSHMEM_TRACE_MAX_EVENTS)
+enum {
+  BSHMEM_TRACE_PUT = 1, BSHMEM_TRACE_GET, BSHMEM_TRACE_PUT_SIGNAL, BSHMEM_TRACE_AMO, BSHMEM_TRACE_WAIT, BSHMEM_TRACE_BARRIER,
+  BSHMEM_TRACE_COLL, BSHMEM_TRACE_TIMEOUT
+};
+
 #ifdef __CUDACC__
 namespace bshmem {
 namespace dev {
@@ -83,6 +94,18 @@ __device__ __forceinline__ int my_pe(const State& s) { return s.my_pe; }
 __device__ __forceinline__ int n_pes(const State& s) { return s.n_pes; }
 __device__ __forceinline__ void stat(const State& s, int idx, unsigned long long by = 1) {
   if (s.stats) atomicAdd(&s.stats[idx], by);
+}
+// One timeline event (who, what, how much, when); a no-op unless the host switched tracing on.
+__device__ __forceinline__ void trace(const State& s, int op, int pe, unsigned long long bytes) {
+  if (!s.stats) return;
+  const unsigned long long cap = *reinterpret_cast<volatile unsigned long long*>(&s.stats[BSHMEM_DSTAT_COUNT]);
+  if (!cap) return;
+  const unsigned long long i = atomicAdd(&s.stats[BSHMEM_DSTAT_COUNT + 1], 1ull);
+  unsigned long long* e = s.stats + BSHMEM_DSTAT_COUNT + 2 + 4 * (i % cap);
+  e[0] = timer();
+  e[1] = (unsigned long long)(op & 0xFF) | ((unsigned long long)(pe & 0xFFFFFF) << 8) | ((unsigned long long)blockIdx.x << 32);
+  e[2] = bytes;
+  e[3] = i;
 }
 __device__ __forceinline__ int team_pe(const Team& t, int idx) { return t.pe_start + idx * t.stride; }
 // world PE -> index in team, -1 if not a member
@@ -118,6 +141,7 @@ __device__ __forceinline__ void record_error(const State& s, uint32_t code, int 
     s.err->code = code;
   }
   stat(s, BSHMEM_DSTAT_TIMEOUTS);
+  trace(s, BSHMEM_TRACE_TIMEOUT, pe, where);
 }
 
 // Debug-build argument check: records BSHMEM_ERR_RANGE and tells the caller to skip the access.
@@ -200,20 +224,20 @@ __device__ __forceinline__ void putmem(const State& s, void* dest, const void* s
   if (n == 0 || !check_target(s, dest, n, pe)) return;
   copy_bytes<S>(reinterpret_cast<char*>(ptr(s, reinterpret_cast<char*>(dest), pe)), reinterpret_cast<const char*>(src), n);
   if (!(ctx_options & BSHMEM_CTX_NOSTORE)) __threadfence();
-  if (scope_rank<S>() == 0) { stat(s, BSHMEM_DSTAT_PUT); stat(s, BSHMEM_DSTAT_BYTES_PUT, n); }
+  if (scope_rank<S>() == 0) { stat(s, BSHMEM_DSTAT_PUT); stat(s, BSHMEM_DSTAT_BYTES_PUT, n); trace(s, BSHMEM_TRACE_PUT, pe, n); }
   scope_sync<S>();
 }
 template <Scope S = THREAD>
 __device__ __forceinline__ void putmem_nbi(const State& s, void* dest, const void* src, size_t n, int pe) {
   if (n == 0 || !check_target(s, dest, n, pe)) return;
   copy_bytes<S>(reinterpret_cast<char*>(ptr(s, reinterpret_cast<char*>(dest), pe)), reinterpret_cast<const char*>(src), n);
-  if (scope_rank<S>() == 0) { stat(s, BSHMEM_DSTAT_PUT); stat(s, BSHMEM_DSTAT_BYTES_PUT, n); }
+  if (scope_rank<S>() == 0) { stat(s, BSHMEM_DSTAT_PUT); stat(s, BSHMEM_DSTAT_BYTES_PUT, n); trace(s, BSHMEM_TRACE_PUT, pe, n); }
 }
 template <Scope S = THREAD>
 __device__ __forceinline__ void getmem(const State& s, void* dest, const void* src, size_t n, int pe) {
   if (n == 0 || !check_target(s, src, n, pe)) return;
   copy_bytes<S>(reinterpret_cast<char*>(dest), reinterpret_cast<const char*>(ptr(s, reinterpret_cast<const char*>(src), pe)), n);
-  if (scope_rank<S>() == 0) { stat(s, BSHMEM_DSTAT_GET); stat(s, BSHMEM_DSTAT_BYTES_GET, n); }
+  if (scope_rank<S>() == 0) { stat(s, BSHMEM_DSTAT_GET); stat(s, BSHMEM_DSTAT_BYTES_GET, n); trace(s, BSHMEM_TRACE_GET, pe, n); }
   scope_sync<S>();
 }
 template <Scope S = THREAD>
@@ -250,6 +274,7 @@ __device__ __forceinline__ void putmem_signal(const State& s, void* dest, const 
     if (sig_op == BSHMEM_SIGNAL_ADD) asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(rs), "l"(signal) : "memory");
     else asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(rs), "l"(signal) : "memory");
     stat(s, BSHMEM_DSTAT_PUT_SIGNAL);
+    trace(s, BSHMEM_TRACE_PUT_SIGNAL, pe, n);
     stat(s, BSHMEM_DSTAT_BYTES_PUT, n);
   }
 }
@@ -380,7 +405,7 @@ __device__ __forceinline__ int wait_until(const State& s, const T* ivar, int cmp
       __nanosleep(64);
     }
   }
-  if (s.stats) { stat(s, BSHMEM_DSTAT_WAIT); stat(s, BSHMEM_DSTAT_WAIT_NS, timer() - t0); }
+  if (s.stats) { stat(s, BSHMEM_DSTAT_WAIT); stat(s, BSHMEM_DSTAT_WAIT_NS, timer() - t0); trace(s, BSHMEM_TRACE_WAIT, s.my_pe, timer() - t0); }
   return BSHMEM_OK;
 }
 

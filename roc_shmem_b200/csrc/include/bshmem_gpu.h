@@ -64,6 +64,9 @@ int bshmem_gpu_get_state(bshmem_handle_t h, bshmem_dev_state_t* out);
 int bshmem_gpu_check_error(bshmem_handle_t h);
 int bshmem_gpu_get_device_stats(bshmem_handle_t h, uint64_t* out, int n);
 int bshmem_gpu_reset_device_stats(bshmem_handle_t h);
+/* Device timeline (event ring behind the counters): capacity 0 = off, at most BSHMEM_TRACE_MAX_EVENTS. */
+int bshmem_gpu_trace_enable(bshmem_handle_t h, int capacity);
+int bshmem_gpu_trace_read(bshmem_handle_t h, uint64_t* out, int max_events, int* n_out, uint64_t* total);
 int bshmem_gpu_rma_kernel(bshmem_handle_t h, void* sym, void* local, uint64_t n, int pe, int is_put, int scope,
                           int ctas, int threads);
 int bshmem_gpu_group_collective(bshmem_handle_t* handles, int n, int team_slot, int kind, int dtype, int op, int root,

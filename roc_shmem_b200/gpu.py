@@ -43,6 +43,8 @@ class DevState(C.Structure):
 DSTAT_NAMES = ("put", "get", "put_signal", "p", "g", "amo", "fence", "quiet", "wait", "wait_ns", "barrier",
                "barrier_ns", "coll", "bytes_put", "bytes_get", "timeouts", "proxy_ops")
 
+TRACE_OPS = {1: "put", 2: "get", 3: "put_signal", 4: "amo", 5: "wait", 6: "barrier", 7: "coll", 8: "timeout"}
+
 COLL_SYNC, COLL_BARRIER, COLL_BROADCAST, COLL_REDUCE, COLL_REDUCE_SCATTER, COLL_FCOLLECT, COLL_ALLTOALL = range(7)
 
 
@@ -78,6 +80,8 @@ def cuda_lib() -> C.CDLL:
         f("bshmem_gpu_check_error", _I, _VP)
         f("bshmem_gpu_get_device_stats", _I, _VP, C.POINTER(_U64), _I)
         f("bshmem_gpu_reset_device_stats", _I, _VP)
+        f("bshmem_gpu_trace_enable", _I, _VP, _I)
+        f("bshmem_gpu_trace_read", _I, _VP, C.POINTER(_U64), _I, C.POINTER(_I), C.POINTER(_U64))
         f("bshmem_gpu_rma_kernel", _I, _VP, _VP, _VP, _U64, _I, _I, _I, _I, _I)
         f("bshmem_gpu_group_collective", _I, C.POINTER(_VP), _I, _I, _I, _I, _I, _I, _U64, _U64, _U64, _I)
         f("bshmem_gpu_group_team_split", _I, C.POINTER(_VP), _I, _I, _I, _I, _I, C.POINTER(_I))
@@ -165,6 +169,24 @@ class DeviceRuntime(Runtime):
 
     def reset_device_stats(self) -> None:
         self._check(self.lib.bshmem_gpu_reset_device_stats(self.h))
+
+    def trace_enable(self, capacity: int = 4096) -> None:
+        """Record a device-side timeline of the last `capacity` (<= 16384) communication events; 0 switches it off.
+        Needs profile=True (the default).  The reference only has counters (library/src/stats.hpp:121-145)."""
+        self._check(self.lib.bshmem_gpu_trace_enable(self.h, capacity))
+
+    def trace_events(self, max_events: int = 16384) -> list:
+        """Events recorded since trace_enable(), oldest first: dicts of t_ns (%globaltimer), op, pe, block, bytes
+        (for waits and barriers: the nanoseconds spent; for timeouts: the site code) and seq."""
+        buf = (C.c_uint64 * (4 * max_events))()
+        n, total = C.c_int(0), C.c_uint64(0)
+        self._check(self.lib.bshmem_gpu_trace_read(self.h, buf, max_events, C.byref(n), C.byref(total)))
+        out = []
+        for k in range(n.value):
+            t, w, b, seq = (int(buf[4 * k + i]) for i in range(4))
+            out.append({"t_ns": t, "op": TRACE_OPS.get(w & 0xFF, str(w & 0xFF)), "pe": (w >> 8) & 0xFFFFFF, "block": w >> 32,
+                        "bytes": b, "seq": seq})
+        return out
 
     def rma_kernel(self, sym: torch.Tensor, local: torch.Tensor, pe: int, *, put: bool = True, scope: str = "block",
                    ctas: int = 32, threads: int = 512, nbytes: Optional[int] = None) -> None:

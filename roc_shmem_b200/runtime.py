@@ -397,3 +397,10 @@ class Runtime:
 
     def dump_stats(self) -> None:
         self._check(self.lib.bshmem_dump_stats(self.h))
+
+
+# NVTX ranges around the host API when B200SHMEM_TRACE=1 (utils/trace.py)
+from .utils.trace import instrument as _instrument  # noqa: E402
+
+_instrument(Runtime, ("put", "get", "put_signal", "barrier_all", "sync_all", "quiet", "fence", "wait_until", "broadcast", "reduce",
+                      "reduce_scatter", "fcollect", "alltoall", "malloc", "free", "team_split_strided", "ctx_create"))

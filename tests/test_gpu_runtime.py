@@ -243,3 +243,29 @@ def test_device_rma_matrix_sizes_and_alignments(rt, scope, put):
                 assert torch.equal(dst[lo:hi], src[256 + o_src:256 + o_src + nbytes]), (scope, put, ctas, nbytes, off_sym, off_loc)
                 assert bool((dst[:lo] == 0xEE).all()) and bool((dst[hi:] == 0xEE).all()), "guard bytes touched"
     rt.free(sym)
+
+
+def test_device_timeline_records_puts_and_waits(rt):
+    """The event ring behind the device counters: off by default, keeps the last `capacity` events in order."""
+    sym = rt.zeros((1 << 16,), torch.uint8)
+    src = torch.ones(1 << 16, dtype=torch.uint8, device="cuda")
+    rt.trace_enable(0)
+    rt.rma_kernel(sym, src, 0, put=True, scope="block", ctas=4, threads=128)
+    rt.quiet()
+    assert rt.trace_events() == []
+    rt.trace_enable(8)
+    rt.rma_kernel(sym, src, 0, put=True, scope="block", ctas=4, threads=128)       # 4 put events (one per CTA)
+    rt.rma_kernel(sym, src, 0, put=False, scope="block", ctas=2, threads=128)      # 2 get events
+    rt.quiet()
+    ev = rt.trace_events()
+    assert [e["op"] for e in ev].count("put") == 4 and [e["op"] for e in ev].count("get") == 2
+    assert sorted(e["block"] for e in ev if e["op"] == "put") == [0, 1, 2, 3]
+    assert all(e["pe"] == 0 and e["bytes"] == (1 << 16) // (4 if e["op"] == "put" else 2) for e in ev)
+    assert [e["seq"] for e in ev] == list(range(6)) and all(ev[i]["t_ns"] <= ev[i + 1]["t_ns"] + 10_000_000 for i in range(5))
+    for _ in range(3):                                                             # overflow: the ring keeps the last 8
+        rt.rma_kernel(sym, src, 0, put=True, scope="block", ctas=4, threads=128)
+    rt.quiet()
+    ev = rt.trace_events()
+    assert len(ev) == 8 and [e["seq"] for e in ev] == list(range(10, 18))
+    rt.trace_enable(0)
+    rt.free(sym)
