@@ -119,9 +119,38 @@ def main() -> None:
     roof2 = max(flops2 / (args.peak_tflops * 1e12), link2 / (args.link_gbs * 1e9)) * 1e3
     results.update({"ag_ms_fused": ms_f2, "ag_ms_nccl_cublas": ms_b2, "ag_speedup": ms_b2 / ms_f2, "ag_roofline_ms": roof2,
                     "ag_roofline_frac": roof2 / ms_f2, "ag_ok": bool(ok_ag)})
+    x_shard_bf16 = ag.x_shard.clone()
     ag.close()
 
-    oks = torch.tensor([int(ok_rs and ok_ag)], device=dev)
+    # ---------------- all-gather -> GEMM on block-scaled fp8 (e4m3 rows cross NVLink: half the bytes) ----------------
+    from roc_shmem_b200.ops.gemm_fp8 import AllGatherGemmFp8, gemm_fp8, quantize_act, quantize_weight
+    ok_ag8 = True
+    if N % 256 == 0 and H % 128 == 0 and (M // P) % 128 == 0:
+        ag8 = AllGatherGemmFp8(rt, M, N, H)
+        qw = quantize_weight(w2)
+        ag8.set_input(x_shard_bf16)
+        rt.barrier_all()
+        ag8(qw)
+        dist.all_gather_into_tensor(gathered, x_shard_bf16)
+        qa_full = quantize_act(gathered)                          # same quantiser on the same rows: identical operands
+        ref8 = gemm_fp8(qa_full, qw)
+        torch.cuda.synchronize()
+        ag8.check()
+        diff8 = (ag8.out.float() - ref8.float()).abs().max().item()
+        gather8_exact = bool(torch.equal(ag8.xq, qa_full.q) and torch.equal(ag8.sa, qa_full.scales))
+        ok_ag8 = diff8 == 0.0 and gather8_exact
+
+        def step8():
+            ag8.set_input(x_shard_bf16)                           # the quantisation of the local rows is part of the step
+            ag8(qw)
+        ms_f8 = timed(step8, args.iters, rt)
+        ag8.check()
+        results.update({"ag_fp8_max_abs_diff_vs_unfused_fp8": diff8, "ag_fp8_gather_exact": gather8_exact, "ag_fp8_ms_fused": ms_f8,
+                        "ag_fp8_speedup_vs_bf16_nccl_cublas": ms_b2 / ms_f8, "ag_fp8_speedup_vs_bf16_fused": ms_f2 / ms_f8,
+                        "ag_fp8_vs_bf16_max_abs_diff": (ag8.out.float() - ref2.float()).abs().max().item(), "ag_fp8_ok": bool(ok_ag8)})
+        ag8.close()
+
+    oks = torch.tensor([int(ok_rs and ok_ag and ok_ag8)], device=dev)
     dist.all_reduce(oks, op=dist.ReduceOp.MIN)
     results["all_ranks_ok"] = bool(oks.item())
     if rank == 0:

@@ -20,6 +20,7 @@
 // Every wait is bounded (see gemm_core.cuh); there is no counterpart in the reference.
 #include <cuda_fp8.h>
 
+#include "../include/bshmem_device.cuh"
 #include "gemm_core.cuh"
 #include "tma_host.h"
 
@@ -40,12 +41,119 @@ constexpr uint32_t kIdescFp8 = ptx::umma_idesc(0, 0, 128, 256);   // e4m3 x e4m3
 
 enum : int { ERR_F8_PART_FULL = 121, ERR_F8_PART_EMPTY = 122 };
 
+constexpr int kMaxPes = BSHMEM_MAX_PES;
+constexpr int kPieceBytes = 16384;
+constexpr int FPULL_WARPS = 2;                          // all-gather variant: warps 18-19 pull the peers' rows
+
+// All-gather state (all-gather -> GEMM variant): the activations A8 [M, K] and their scales [K/128][M] live in
+// symmetric memory; every PE owns M/P rows.  Pull warps copy the peers' rows and scale columns into the local
+// buffers piece by piece (a piece = up to 16 KiB of one row, or the scale columns of one 128-row block) and bump
+// the block's arrival counter; producers and epilogue warps wait on that counter before they touch the block.
+struct Fp8Ag {
+  int P, my_rank, blocks_per_rank, pieces_per_row;
+  int pieces_per_block, pieces_per_src, total_pieces, num_kb;
+  unsigned long long row_bytes;
+  const char* xq_peer[kMaxPes];
+  char* xq_local;
+  const float* sa_peer[kMaxPes];
+  float* sa_local;
+  unsigned long long* arrived;                  // local [M/128]: pieces landed (monotonic over calls)
+  unsigned long long* src_pulled;               // local [P]
+  unsigned int* ticket;                         // local [2]: work counter of this call's parity
+  unsigned long long* ready_remote[kMaxPes];    // peer's ready[P]; this rank writes entry my_rank
+  const unsigned long long* ready_local;
+  unsigned long long* done_remote[kMaxPes];
+  const unsigned long long* done_local;
+  unsigned long long call;
+};
+
 struct Fp8Params {
   CoreParams core;             // num_m_blocks counts 128-row blocks
   CUtensorMap map_a, map_b, map_c;
   const float* sa;             // [K/128][M]
   const float* sb;             // [K/128][N/128]
+  Fp8Ag ag;                    // used by the all-gather variant only
 };
+
+enum : int { ERR_F8_A_READY = 123, ERR_F8_PEER_READY = 124, ERR_F8_PEER_DONE = 125 };
+
+// Tile order: grouped raster, or (all-gather) source-major starting with this PE's own rows, then the rows of
+// rank me+1, me+2, ... which is also the order in which the pull warps fetch them.
+template <bool kAG>
+__device__ __forceinline__ void f8_tile_coords(const Fp8Params& p, int tile, int* m_blk, int* n_blk) {
+  if constexpr (!kAG) {
+    raster_coords(p.core, tile, m_blk, n_blk);
+  } else {
+    const int per_src = p.ag.blocks_per_rank * p.core.num_n_blocks;
+    const int step = tile / per_src, rem = tile - step * per_src;
+    const int src = (p.ag.my_rank + step) % p.ag.P;
+    *m_blk = src * p.ag.blocks_per_rank + rem % p.ag.blocks_per_rank;
+    *n_blk = rem / p.ag.blocks_per_rank;
+  }
+}
+
+// One pull warp fetches one piece; returns false when no work is left (or the CTA is aborting).
+__device__ __forceinline__ bool f8_pull_piece(const Fp8Params& prm, int lane, Guard& g) {
+  const Fp8Ag& p = prm.ag;
+  unsigned int t = 0;
+  if (lane == 0) t = atomicAdd(&p.ticket[p.call & 1], 1u);
+  t = __shfl_sync(0xffffffffu, t, 0);
+  if (t >= (unsigned)p.total_pieces) return false;
+  const int step = t / p.pieces_per_src, rem = t - step * p.pieces_per_src;
+  const int blk_in_src = rem / p.pieces_per_block, piece = rem - blk_in_src * p.pieces_per_block;
+  const int src = (p.my_rank + 1 + step) % p.P;
+  const int m_blk = src * p.blocks_per_rank + blk_in_src;
+  int ok = 1;
+  if (lane == 0) ok = wait_ge<true>(p.ready_local + src, p.call, g, ERR_F8_PEER_READY) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (!ok) return false;
+  if (piece < p.pieces_per_block - 1) {
+    // up to 16 KiB of one activation row
+    const int row = piece / p.pieces_per_row, seg = piece - row * p.pieces_per_row;
+    const unsigned long long off = ((unsigned long long)m_blk * FBM + row) * p.row_bytes + (unsigned long long)seg * kPieceBytes;
+    const unsigned long long left = p.row_bytes - (unsigned long long)seg * kPieceBytes;
+    const int nvec = (int)((left < (unsigned long long)kPieceBytes ? left : (unsigned long long)kPieceBytes) >> 4);
+    const uint4* s4 = reinterpret_cast<const uint4*>(p.xq_peer[src] + off);
+    uint4* d4 = reinterpret_cast<uint4*>(p.xq_local + off);
+    int i = lane;
+    for (; i + 224 < nvec; i += 256) {                  // eight independent 16-byte peer loads in flight per lane
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = ptx::ld_relaxed_v4(s4 + i + 32 * u);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) d4[i + 32 * u] = v[u];
+    }
+    for (; i < nvec; i += 32) d4[i] = ptx::ld_relaxed_v4(s4 + i);
+  } else {
+    // the block's scale columns: 128 floats (512 bytes) of every k-block row of the [K/128][M] scale matrix
+    const size_t col0 = (size_t)m_blk * FBM;
+    int kb = 0;
+    for (; kb + 8 <= p.num_kb; kb += 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        v[u] = ptx::ld_relaxed_v4(reinterpret_cast<const uint4*>(p.sa_peer[src] + (size_t)(kb + u) * prm.core.M + col0) + lane);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) reinterpret_cast<uint4*>(p.sa_local + (size_t)(kb + u) * prm.core.M + col0)[lane] = v[u];
+    }
+    for (; kb < p.num_kb; ++kb)
+      reinterpret_cast<uint4*>(p.sa_local + (size_t)kb * prm.core.M + col0)[lane] =
+          ptx::ld_relaxed_v4(reinterpret_cast<const uint4*>(p.sa_peer[src] + (size_t)kb * prm.core.M + col0) + lane);
+  }
+  ptx::fence_proxy_async_all();           // generic-proxy stores (the pull) before async-proxy reads (TMA)
+  __syncwarp();
+  if (lane == 0) {
+    __threadfence();
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p.arrived + m_blk), "l"(1ull) : "memory");
+    const unsigned long long pulled = atomicAdd(p.src_pulled + src, 1ull) + 1;
+    if (pulled == (unsigned long long)p.pieces_per_src * p.call) {
+      // everything of `src` is here: it may overwrite its rows once every PE said so
+      ptx::fence_acq_rel_sys();
+      ptx::st_release_sys_u64(reinterpret_cast<uint64_t*>(p.done_remote[src] + p.my_rank), p.call);
+    }
+  }
+  return true;
+}
 
 struct FSmem {
   uint32_t base;
@@ -64,8 +172,8 @@ struct FSmem {
   }
 };
 
-__global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(const __grid_constant__ Fp8Params prm) {
-  extern __shared__ uint8_t smem_raw[];
+template <bool kAG>
+__device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, uint8_t* smem_raw) {
   FSmem L;
   {
     uint32_t r = ptx::smem_u32(smem_raw);
@@ -95,15 +203,38 @@ __global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(co
   ptx::tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(L.tmem_slot()));
+  if constexpr (kAG) {
+    // one thread of CTA 0: recycle the other parity's ticket counter and tell every peer that this PE's rows and
+    // scales are in place for this call (they were written by earlier work on the stream)
+    if (blockIdx.x == 0 && threadIdx.x == 64) {
+      prm.ag.ticket[(prm.ag.call + 1) & 1] = 0;
+      ptx::fence_acq_rel_sys();
+      for (int q = 0; q < prm.ag.P; ++q)
+        if (q != prm.ag.my_rank)
+          ptx::st_release_sys_u64(reinterpret_cast<uint64_t*>(prm.ag.ready_remote[q] + prm.ag.my_rank), prm.ag.call);
+    }
+  }
 
-  if (warp == 0) {
+  if (warp >= 2 + FEPI_WARPS) {
+    // ------------------------------ pull warps (all-gather variant) ------------
+    if constexpr (kAG) {
+      if (prm.ag.P > 1)
+        while (f8_pull_piece(prm, lane, g)) {}
+    }
+  } else if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int s = 0; uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
-        raster_coords(cp, tile, &m_blk, &n_blk);
+        f8_tile_coords<kAG>(prm, tile, &m_blk, &n_blk);
+        if constexpr (kAG) {
+          if (m_blk / prm.ag.blocks_per_rank != prm.ag.my_rank) {
+            if (!wait_ge<false>(prm.ag.arrived + m_blk, (unsigned long long)prm.ag.pieces_per_block * prm.ag.call, g, ERR_F8_A_READY)) break;
+            ptx::fence_proxy_async_all();
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(L.empty(s), ph ^ 1, g, ERR_PRODUCER_EMPTY)) { ok = false; break; }
           ptx::mbar_arrive_expect_tx(L.full(s), FSTAGE_BYTES);
@@ -146,7 +277,17 @@ __global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(co
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_blk, n_blk;
-      raster_coords(cp, tile, &m_blk, &n_blk);
+      f8_tile_coords<kAG>(prm, tile, &m_blk, &n_blk);
+      if constexpr (kAG) {
+        // the block's scale columns are pulled like its rows: wait for them before the first scale load
+        if (m_blk / prm.ag.blocks_per_rank != prm.ag.my_rank) {
+          int arrived_ok = 1;
+          if (lane == 0)
+            arrived_ok = wait_ge<false>(prm.ag.arrived + m_blk, (unsigned long long)prm.ag.pieces_per_block * prm.ag.call, g, ERR_F8_A_READY) ? 1 : 0;
+          arrived_ok = __shfl_sync(0xffffffffu, arrived_ok, 0);
+          if (!arrived_ok) { ok = false; break; }
+        }
+      }
       const int row = m_blk * FBM + quarter * 32 + lane;
       const float* sa = prm.sa + row;
       const float* sb = prm.sb + (n_blk * (FBN / 128) + (cg >> 1));
@@ -156,7 +297,10 @@ __global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(co
       for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.f, 0.f);
       // scales are fetched three k-blocks ahead of their use (an L2 round trip is longer than a k-block)
       auto scale_at = [&](int kb) -> float {
-        return kb < num_kb ? __ldg(sa + (size_t)kb * cp.M) * __ldg(sb + (size_t)kb * sb_stride) : 0.f;
+        if (kb >= num_kb) return 0.f;
+        // pulled scales were written during this kernel: no non-coherent load for them
+        const float a = kAG ? *reinterpret_cast<const volatile float*>(sa + (size_t)kb * cp.M) : __ldg(sa + (size_t)kb * cp.M);
+        return a * __ldg(sb + (size_t)kb * sb_stride);
       };
       float s0 = scale_at(0), s1 = scale_at(1), s2n = scale_at(2);
 #pragma unroll 1
@@ -212,6 +356,12 @@ __global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(co
   // ------------------------------ teardown ---------------------------------------
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (kAG) {
+    // before the kernel ends, CTA 0 makes sure every peer has finished pulling this PE's rows
+    if (!*L.abort_flag() && blockIdx.x == 0 && (int)threadIdx.x < prm.ag.P && (int)threadIdx.x != prm.ag.my_rank)
+      wait_ge<true>(prm.ag.done_local + threadIdx.x, prm.ag.call, g, ERR_F8_PEER_DONE);
+    __syncthreads();
+  }
   if (*L.abort_flag()) {
     // let copies and MMAs that are still in flight land before smem/TMEM go away
     unsigned long long t0 = ptx::globaltimer();
@@ -224,6 +374,16 @@ __global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(co
   }
 }
 
+__global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(const __grid_constant__ Fp8Params prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_fp8_body<false>(prm, smem_raw);
+}
+// all-gather -> GEMM: two more warps per CTA pull the peers' rows and scales while the tensor core runs
+__global__ void __launch_bounds__(FNUM_THREADS + 32 * FPULL_WARPS, 1) ag_gemm_fp8_kernel(const __grid_constant__ Fp8Params prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_fp8_body<true>(prm, smem_raw);
+}
+
 // ---- quantisers ------------------------------------------------------------------------------
 __device__ __forceinline__ uint8_t to_e4m3(float x) {
   return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
@@ -232,7 +392,7 @@ __device__ __forceinline__ uint8_t to_e4m3(float x) {
 // Activations: one scale per row and 128 columns.  One warp per (row, k-block); lane l owns 4 elements.
 // q: [M, K] e4m3, scales: [K/128][M] fp32 with  x ≈ q * scale,  scale = absmax / 448 (1 if the block is all zero).
 __global__ void quant_act_1x128_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int ldx, uint8_t* __restrict__ q,
-                                       float* __restrict__ scales) {
+                                       float* __restrict__ scales, int scale_ld) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long nblk = (long long)M * (K / 128);
@@ -249,7 +409,7 @@ __global__ void quant_act_1x128_kernel(const __nv_bfloat16* __restrict__ x, int 
     const float inv = 1.f / scale;
     uint32_t packed = to_e4m3(v[0] * inv) | (to_e4m3(v[1] * inv) << 8) | (to_e4m3(v[2] * inv) << 16) | ((uint32_t)to_e4m3(v[3] * inv) << 24);
     *reinterpret_cast<uint32_t*>(q + (size_t)m * K + kb * 128 + lane * 4) = packed;
-    if (lane == 0) scales[(size_t)kb * M + m] = scale;
+    if (lane == 0) scales[(size_t)kb * scale_ld + m] = scale;
   }
 }
 
@@ -304,12 +464,35 @@ __global__ void quant_w_128x128_kernel(const __nv_bfloat16* __restrict__ w, int 
 int* g_err_dev[64] = {};
 int g_sms[64] = {};
 
+struct AgPlan {
+  bshmem_dev_state_t st;
+  int M, N, K, device;
+  unsigned long long call = 0;
+  int* err = nullptr;
+  char* xq_local = nullptr;                    // symmetric [M, K] e4m3
+  float* sa_local = nullptr;                   // symmetric [K/128][M]
+  unsigned long long* flags_local = nullptr;   // symmetric: ready[P] then done[P]
+  unsigned long long* arrived = nullptr;
+  unsigned long long* src_pulled = nullptr;
+  unsigned int* ticket = nullptr;
+};
+
+template <typename T> T* peer_ptr(const bshmem_dev_state_t& st, T* local, int pe) {
+  return reinterpret_cast<T*>(st.heap_base[pe] + (reinterpret_cast<char*>(local) - st.heap_base[st.my_pe]));
+}
+bool in_heap(const bshmem_dev_state_t& st, const void* p, uint64_t n) {
+  const char* c = static_cast<const char*>(p);
+  const char* b = st.heap_base[st.my_pe];
+  return c >= b && (uint64_t)(c - b) + n <= st.heap_bytes;
+}
+
 int ensure(int dev) {
   if (g_err_dev[dev]) return 0;
   BSHMEM_CUDA_TRY(cudaMalloc(&g_err_dev[dev], sizeof(int)));
   BSHMEM_CUDA_TRY(cudaMemset(g_err_dev[dev], 0, sizeof(int)));
   BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(gemm_fp8_blockscale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FSMEM_BYTES));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(ag_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FSMEM_BYTES));
   return 0;
 }
 
@@ -354,15 +537,121 @@ int bshmem_gemm_fp8_blockscale(const void* A8, const float* scale_a, const void*
   return 0;
 }
 
-// x: [M, K] bf16 (ldx elements, % 4 == 0, 8-byte aligned rows) -> q [M, K] e4m3 + scales [K/128][M].
-int bshmem_fp8_quant_act(const void* x, int M, int K, int ldx, void* q, float* scales, void* stream) {
-  if (K % 128 || ldx % 4) { host::last_error() = "fp8 quant: K % 128 != 0 or ldx % 4 != 0"; return 1; }
+// x: [M, K] bf16 (ldx elements, % 4 == 0, 8-byte aligned rows) -> q [M, K] e4m3 + scales; the scale of row m and
+// k-block kb goes to scales[kb * scale_ld + m] (scale_ld >= M: a shard can write its columns of a wider matrix).
+int bshmem_fp8_quant_act_ld(const void* x, int M, int K, int ldx, void* q, float* scales, int scale_ld, void* stream) {
+  if (K % 128 || ldx % 4 || scale_ld < M) { host::last_error() = "fp8 quant: K % 128 != 0, ldx % 4 != 0 or scale_ld < M"; return 1; }
   long long nblk = (long long)M * (K / 128);
   int blocks = (int)((nblk + 7) / 8 < 148 * 16 ? (nblk + 7) / 8 : 148 * 16);
   if (blocks < 1) blocks = 1;
   quant_act_1x128_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x), M, K, ldx,
-                                                                                static_cast<uint8_t*>(q), scales);
+                                                                                static_cast<uint8_t*>(q), scales, scale_ld);
   BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+int bshmem_fp8_quant_act(const void* x, int M, int K, int ldx, void* q, float* scales, void* stream) {
+  return bshmem_fp8_quant_act_ld(x, M, K, ldx, q, scales, M, stream);
+}
+
+// ---- all-gather -> fp8 GEMM -------------------------------------------------------------------------------
+// Symmetric memory of a plan: xq [M, K] bytes, sa [K/128][M] floats, 2*P flag words (zeroed, then a barrier).
+uint64_t bshmem_fp8_ag_flag_bytes(int P) { return 2ull * P * 8; }
+
+int bshmem_fp8_ag_plan(const bshmem_dev_state_t* st, int M, int N, int K, void* xq_local, void* sa_local, void* flags_local, void** out) {
+  if (!st || !out) return 1;
+  const int P = st->n_pes;
+  if (P > kMaxPes || M % (P * FBM) || N % FBN || K % FBK) {
+    host::last_error() = "ag_gemm_fp8: needs M % (P*128) == 0, N % 256 == 0, K % 128 == 0";
+    return 1;
+  }
+  if (!in_heap(*st, xq_local, (uint64_t)M * K) || !in_heap(*st, sa_local, (uint64_t)(K / 128) * M * 4) ||
+      !in_heap(*st, flags_local, bshmem_fp8_ag_flag_bytes(P))) {
+    host::last_error() = "ag_gemm_fp8: the gathered activations, their scales and the flags must be symmetric allocations";
+    return 4;
+  }
+  AgPlan* p = new AgPlan();
+  p->st = *st; p->M = M; p->N = N; p->K = K;
+  p->xq_local = static_cast<char*>(xq_local);
+  p->sa_local = static_cast<float*>(sa_local);
+  p->flags_local = static_cast<unsigned long long*>(flags_local);
+  BSHMEM_CUDA_TRY(cudaGetDevice(&p->device));
+  int rc = ensure(p->device);
+  if (rc) { delete p; return rc; }
+  const int nblk = M / FBM;
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->err, sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaMemset(p->err, 0, sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->arrived, sizeof(unsigned long long) * nblk));
+  BSHMEM_CUDA_TRY(cudaMemset(p->arrived, 0, sizeof(unsigned long long) * nblk));
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->src_pulled, sizeof(unsigned long long) * kMaxPes));
+  BSHMEM_CUDA_TRY(cudaMemset(p->src_pulled, 0, sizeof(unsigned long long) * kMaxPes));
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->ticket, sizeof(unsigned int) * 2));
+  BSHMEM_CUDA_TRY(cudaMemset(p->ticket, 0, sizeof(unsigned int) * 2));
+  *out = p;
+  return 0;
+}
+
+// This PE's quantised rows and scale columns must already be in place (bshmem_fp8_quant_act_ld into the shard's slice).
+// B8: [N, K] e4m3, scale_b: [K/128][N/128], C: [M, N] bf16 (ldc).
+int bshmem_fp8_ag_run(void* plan, const void* B8, const float* scale_b, void* C, int ldc, void* stream, int timeout_ms, int max_ctas) {
+  AgPlan* p = static_cast<AgPlan*>(plan);
+  if (!p || ldc % 8) return 1;
+  const int P = p->st.n_pes, me = p->st.my_pe;
+  p->call += 1;
+  Fp8Params prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.core.M = p->M; prm.core.N = p->N; prm.core.K = p->K;
+  prm.core.num_m_blocks = p->M / FBM; prm.core.num_n_blocks = p->N / FBN;
+  prm.core.group_m = 32;
+  prm.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  prm.core.err = p->err;
+  prm.sa = p->sa_local; prm.sb = scale_b;
+  Fp8Ag& a = prm.ag;
+  a.P = P; a.my_rank = me; a.blocks_per_rank = p->M / P / FBM;
+  a.row_bytes = (unsigned long long)p->K;
+  a.num_kb = p->K / FBK;
+  a.pieces_per_row = (int)((a.row_bytes + kPieceBytes - 1) / kPieceBytes);
+  a.pieces_per_block = FBM * a.pieces_per_row + 1;                 // + the block's scale columns
+  a.pieces_per_src = a.blocks_per_rank * a.pieces_per_block;
+  a.total_pieces = (P - 1) * a.pieces_per_src;
+  int rc = host::make_tmap_2d(&prm.map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p->xq_local, p->M, p->K, p->K, FBM, FBK);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&prm.map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B8, p->N, p->K, p->K, FBN, FBK);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&prm.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, p->M, p->N, ldc, 32, 64);
+  if (rc) return rc;
+  for (int q = 0; q < P; ++q) {
+    a.xq_peer[q] = peer_ptr(p->st, p->xq_local, q);
+    a.sa_peer[q] = peer_ptr(p->st, p->sa_local, q);
+    a.ready_remote[q] = peer_ptr(p->st, p->flags_local, q);
+    a.done_remote[q] = peer_ptr(p->st, p->flags_local, q) + P;
+  }
+  a.xq_local = p->xq_local; a.sa_local = p->sa_local;
+  a.arrived = p->arrived; a.src_pulled = p->src_pulled; a.ticket = p->ticket;
+  a.ready_local = p->flags_local; a.done_local = p->flags_local + P;
+  a.call = p->call;
+  int ctas = g_sms[p->device];
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  const int tiles = prm.core.num_m_blocks * prm.core.num_n_blocks;
+  if (ctas > tiles) ctas = tiles;
+  ag_gemm_fp8_kernel<<<ctas, FNUM_THREADS + 32 * FPULL_WARPS, FSMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(prm);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int bshmem_fp8_ag_error_site(void* plan, int clear) {
+  AgPlan* p = static_cast<AgPlan*>(plan);
+  int v = 0;
+  if (!p || !p->err) return 0;
+  cudaMemcpy(&v, p->err, sizeof(int), cudaMemcpyDeviceToHost);
+  if (clear && v) cudaMemset(p->err, 0, sizeof(int));
+  return v;
+}
+
+int bshmem_fp8_ag_destroy(void* plan) {
+  AgPlan* p = static_cast<AgPlan*>(plan);
+  if (!p) return 0;
+  cudaFree(p->err); cudaFree(p->arrived); cudaFree(p->src_pulled); cudaFree(p->ticket);
+  delete p;
   return 0;
 }
 

@@ -32,6 +32,18 @@ def fp8_lib() -> C.CDLL:
         lib.bshmem_fp8_quant_weight.argtypes = [VP, I, I, I, VP, VP, VP]
         lib.bshmem_fp8_error_site.restype = I
         lib.bshmem_fp8_error_site.argtypes = [I]
+        lib.bshmem_fp8_quant_act_ld.restype = I
+        lib.bshmem_fp8_quant_act_ld.argtypes = [VP, I, I, I, VP, VP, I, VP]
+        lib.bshmem_fp8_ag_flag_bytes.restype = C.c_uint64
+        lib.bshmem_fp8_ag_flag_bytes.argtypes = [I]
+        lib.bshmem_fp8_ag_plan.restype = I
+        lib.bshmem_fp8_ag_plan.argtypes = [VP, I, I, I, VP, VP, VP, C.POINTER(VP)]
+        lib.bshmem_fp8_ag_run.restype = I
+        lib.bshmem_fp8_ag_run.argtypes = [VP, VP, VP, VP, I, VP, I, I]
+        lib.bshmem_fp8_ag_error_site.restype = I
+        lib.bshmem_fp8_ag_error_site.argtypes = [VP, I]
+        lib.bshmem_fp8_ag_destroy.restype = I
+        lib.bshmem_fp8_ag_destroy.argtypes = [VP]
         _declared = True
     return lib
 
@@ -111,3 +123,66 @@ def gemm_fp8(a: Fp8Tensor, b: Fp8Tensor, out: Optional[torch.Tensor] = None, *, 
 def fp8_error_site(clear: bool = True) -> int:
     """0 if no in-kernel bounded wait ran out since the last clear, else the site code."""
     return int(fp8_lib().bshmem_fp8_error_site(int(clear)))
+
+
+class AllGatherGemmFp8:
+    """out[M, N] (bf16) = all_gather_rows(quantised activations)[M, K] @ dequant(weight)[N, K].T in ONE kernel:
+    the block-scaled fp8 GEMM whose two extra warps per CTA pull the peers' e4m3 rows and scale columns over
+    NVLink while the tensor core works on rows that have already arrived.  Gathering e4m3 instead of bf16 halves
+    the bytes on the wire.  ``set_input(x_shard)`` quantises this PE's [M/P, K] bf16 rows into its slice of the
+    symmetric buffers; ``__call__(weight)`` runs the kernel on the current stream."""
+
+    algorithm = ("one kernel: block-scaled fp8 tcgen05 GEMM (128x256 tiles, per-k-block promotion) + 2 pull warps per CTA "
+                 "fetching the peers' e4m3 rows and scales over NVLink; producers wait on per-128-row arrival counters")
+
+    def __init__(self, rt, M: int, N: int, K: int, timeout_ms: int = 2000, max_ctas: int = 0):
+        self.rt, self.M, self.N, self.K = rt, M, N, K
+        self.lib = fp8_lib()
+        P = rt.n_pes
+        self.timeout_ms, self.max_ctas = timeout_ms, max_ctas
+        self.xq = rt.empty((M, K), torch.uint8, align=1024)
+        self.sa = rt.empty((K // 128, M), torch.float32, align=1024)
+        self.flags = rt.zeros((2 * P,), torch.int64)
+        self.rows = M // P
+        self.row0 = rt.my_pe * self.rows
+        self.out = torch.empty((M, N), dtype=torch.bfloat16, device=rt.device)
+        st = rt.device_state()
+        plan = C.c_void_p()
+        rc = self.lib.bshmem_fp8_ag_plan(C.byref(st), M, N, K, self.xq.data_ptr(), self.sa.data_ptr(), self.flags.data_ptr(),
+                                         C.byref(plan))
+        if rc != 0:
+            raise RuntimeError(f"ag_gemm_fp8 plan failed ({rc}): {self.lib.bshmem_fp8_last_error().decode()}")
+        self.plan = plan
+        rt.barrier_all()      # every PE's flag words are zero before anyone signals
+
+    def set_input(self, x_shard: torch.Tensor) -> None:
+        """Quantise this PE's rows (bf16 [M/P, K]) into its slice of the gathered e4m3 buffer and scale matrix."""
+        if x_shard.shape != (self.rows, self.K) or x_shard.dtype != torch.bfloat16 or x_shard.stride(1) != 1:
+            raise ValueError("set_input needs this PE's [M/P, K] bf16 rows")
+        q = self.xq[self.row0:self.row0 + self.rows]
+        rc = self.lib.bshmem_fp8_quant_act_ld(x_shard.data_ptr(), self.rows, self.K, x_shard.stride(0), q.data_ptr(),
+                                              self.sa.data_ptr() + 4 * self.row0, self.M, _stream())
+        if rc != 0:
+            raise RuntimeError(f"fp8 quantise failed ({rc}): {self.lib.bshmem_fp8_last_error().decode()}")
+
+    def __call__(self, weight: Fp8Tensor, out: Optional[torch.Tensor] = None) -> int:
+        out = self.out if out is None else out
+        rc = self.lib.bshmem_fp8_ag_run(self.plan, weight.q.data_ptr(), weight.scales.data_ptr(), out.data_ptr(), out.stride(0),
+                                        _stream(), self.timeout_ms, self.max_ctas)
+        if rc != 0:
+            raise RuntimeError(f"ag_gemm_fp8 run failed ({rc}): {self.lib.bshmem_fp8_last_error().decode()}")
+        return 1
+
+    def gathered(self) -> Fp8Tensor:
+        """The local gathered copy (complete after a call)."""
+        return Fp8Tensor(self.xq, self.sa, "act")
+
+    def check(self) -> None:
+        site = self.lib.bshmem_fp8_ag_error_site(self.plan, 1)
+        if site:
+            raise RuntimeError(f"ag_gemm_fp8: a bounded in-kernel wait ran out (site {site})")
+
+    def close(self) -> None:
+        if self.plan:
+            self.lib.bshmem_fp8_ag_destroy(self.plan)
+            self.plan = None

@@ -55,3 +55,28 @@ def test_gemm_fp8_blockscale(M, N, K):
     # and the quantised product stays close to the bf16 one
     full = x.float() @ w.float().t()
     assert (out.float() - full).abs().max().item() <= 0.06 * full.abs().max().item()
+
+
+def test_all_gather_gemm_fp8_single_pe_equals_plain_kernel():
+    """With one PE the fused kernel has nothing to pull: same tiles, same math, bit-identical output; run twice
+    (call-parity counters)."""
+    import roc_shmem_b200 as shmem
+    from roc_shmem_b200.ops.gemm_fp8 import AllGatherGemmFp8, gemm_fp8, quantize_act, quantize_weight
+    rt = shmem.init("device", rank=0, world_size=1, heap_bytes=256 << 20, timeout_ms=5000)
+    try:
+        torch.manual_seed(5)
+        M, N, K = 512, 768, 640
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        qw = quantize_weight((torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16))
+        op = AllGatherGemmFp8(rt, M, N, K)
+        for _ in range(2):
+            op.set_input(x)
+            op(qw)
+        torch.cuda.synchronize()
+        op.check()
+        qa = quantize_act(x)
+        assert torch.equal(op.xq, qa.q) and torch.equal(op.sa, qa.scales)
+        assert torch.equal(op.out, gemm_fp8(qa, qw))
+        op.close()
+    finally:
+        shmem.finalize()
