@@ -254,8 +254,11 @@ int heap_multicast_create(Heap* h, int* fd) {
   if (!h || h->mode != HEAP_VMM || !heap_multicast_supported(h->device)) return BSHMEM_ERR_UNSUPPORTED;
   CUmulticastObjectProp p = mc_prop(h);
   size_t gran = 0;
-  CU_TRY(drv().MulticastGetGranularity(&gran, &p, CU_MULTICAST_GRANULARITY_RECOMMENDED));
-  if (h->heap_bytes % gran) { heap_error() = "heap size is not a multiple of the multicast granularity"; return BSHMEM_ERR_UNSUPPORTED; }
+  CU_TRY(drv().MulticastGetGranularity(&gran, &p, CU_MULTICAST_GRANULARITY_MINIMUM));
+  if (h->heap_bytes % gran) {
+    heap_error() = "heap size " + std::to_string(h->heap_bytes) + " is not a multiple of the multicast granularity " + std::to_string(gran);
+    return BSHMEM_ERR_UNSUPPORTED;
+  }
   CU_TRY(drv().MulticastCreate(&h->mc_handle, &p));
   h->mc_created = true;
   int out = -1;

@@ -385,17 +385,31 @@ __device__ __forceinline__ int team_reduce_nvls(const State& s, const Team& t, T
   uint64_t doff = reinterpret_cast<char*>(dest) - s.heap_base[s.my_pe];
   const char* mc_src = s.mc_base + soff;
   char* mc_dst = s.mc_base + doff;
-  for (size_t v = (sb + b) / VE + threadIdx.x; v < (sb + e) / VE; v += blockDim.x) {
-    uint4 r;
-    if constexpr (std::is_same<T, float>::value) {
-      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                   : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_src + v * 16) : "memory");
-    } else {
-      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                   : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_src + v * 16) : "memory");
+  // eight in-switch reductions in flight per thread: each is a round trip through the NVSwitch
+  constexpr int U = 8;
+  const size_t v1 = (sb + e) / VE;
+  for (size_t base = (sb + b) / VE; base < v1; base += (size_t)U * blockDim.x) {
+    uint4 r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = base + (size_t)u * blockDim.x + threadIdx.x;
+      if (v < v1) {
+        if constexpr (std::is_same<T, float>::value) {
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(r[u].x), "=r"(r[u].y), "=r"(r[u].z), "=r"(r[u].w) : "l"(mc_src + v * 16) : "memory");
+        } else {
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(r[u].x), "=r"(r[u].y), "=r"(r[u].z), "=r"(r[u].w) : "l"(mc_src + v * 16) : "memory");
+        }
+      }
     }
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
-                 ::"l"(mc_dst + v * 16), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = base + (size_t)u * blockDim.x + threadIdx.x;
+      if (v < v1)
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                     ::"l"(mc_dst + v * 16), "r"(r[u].x), "r"(r[u].y), "r"(r[u].z), "r"(r[u].w) : "memory");
+    }
   }
   return team_barrier(s, t, cta);
 }
