@@ -45,6 +45,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--out", default="")
     ap.add_argument("--no-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=8)
+    ap.add_argument("--topk", type=int, default=2)
     args = ap.parse_args()
     rank, P = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -52,7 +54,7 @@ def main() -> None:
     for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533")):
         os.environ.setdefault(k, v)                        # plain `python -m ...` = one rank
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    E, topk = 8, 2
+    E, topk = args.experts, args.topk
     if args.small:
         T, H, F = 1024, 512, 1024
     elif args.mid:
