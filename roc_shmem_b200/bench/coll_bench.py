@@ -41,6 +41,7 @@ def main() -> None:
     ap.add_argument("--out", default="")
     ap.add_argument("--ctas", type=int, default=128)
     ap.add_argument("--nvls", action="store_true")
+    ap.add_argument("--team-sizes", default="", help="comma list: also time allreduce / fcollect on disjoint teams of that many PEs")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -144,6 +145,54 @@ def main() -> None:
         us_n = timed(lambda: dist.all_to_all_single(ref, a_src), iters, rt)
         rows.append({"op": "alltoall", "bytes": blk * P, "us": us, "nccl_us": us_n, "busbw_GBps": (P - 1) * blk / us / 1e3,
                      "ok": bool(good)})
+    # ---- sub-teams: all teams of a size run their collective at the same time (team k = PEs [k*ts, (k+1)*ts)) ----
+    for ts in [int(v) for v in args.team_sizes.split(",") if v]:
+        if ts < 2 or ts >= P or P % ts:
+            continue
+        mine, group = None, None
+        rt.synchronize()
+        rt.set_blocking(True)                          # team creation is a host-synchronous collective
+        for k in range(P // ts):                       # every PE takes part in every split, like every rank in every new_group
+            t = rt.team_split_strided(None, k * ts, 1, ts)
+            g = dist.new_group(list(range(k * ts, (k + 1) * ts)))
+            if t.valid:
+                mine, group = t, g
+        rt.set_blocking(False)
+        us = timed(lambda: mine.sync(), 50, rt)
+        rows.append({"op": "team_sync", "team": ts, "bytes": 0, "us": us})
+        for nbytes in [s_ for s_ in sizes if s_ in (1024, 65536, 1 << 20, 16 << 20, 256 << 20)]:
+            n = nbytes // 4
+            n -= n % ts
+            src = src_all[: n * 4].view(torch.float32)
+            dst = dst_all[: n * 4].view(torch.float32)
+            src.copy_(torch.randn(n, device=dev))
+            ref = src.clone()
+            rt.reduce(dst, src, "sum", team=mine)
+            dist.all_reduce(ref, group=group)
+            torch.cuda.synchronize()
+            good = torch.allclose(dst, ref, rtol=1e-5, atol=1e-4)
+            ok_all &= bool(good)
+            iters = 20 if nbytes <= (16 << 20) else 5
+            us = timed(lambda: rt.reduce(dst, src, "sum", team=mine), iters, rt)
+            us_n = timed(lambda: dist.all_reduce(ref, group=group), iters, rt)
+            rows.append({"op": "allreduce_sum", "team": ts, "dtype": "float32", "bytes": n * 4, "us": us, "nccl_us": us_n,
+                         "busbw_GBps": 2 * (ts - 1) / ts * n * 4 / us / 1e3, "nccl_busbw_GBps": 2 * (ts - 1) / ts * n * 4 / us_n / 1e3,
+                         "ok": bool(good)})
+            blk = (nbytes // ts) - (nbytes // ts) % 16
+            if blk:
+                fsrc, fdst = src_all[:blk], dst_all[: blk * ts]
+                fref = torch.empty(blk * ts, device=dev, dtype=torch.uint8)
+                rt.fcollect(fdst, fsrc, team=mine)
+                dist.all_gather_into_tensor(fref, fsrc, group=group)
+                torch.cuda.synchronize()
+                good = torch.equal(fdst, fref)
+                ok_all &= bool(good)
+                us = timed(lambda: rt.fcollect(fdst, fsrc, team=mine), iters, rt)
+                us_n = timed(lambda: dist.all_gather_into_tensor(fref, fsrc, group=group), iters, rt)
+                rows.append({"op": "fcollect", "team": ts, "bytes": blk * ts, "us": us, "nccl_us": us_n,
+                             "busbw_GBps": (ts - 1) * blk / us / 1e3, "ok": bool(good)})
+        rt.synchronize()
+        mine.destroy()
     rt.synchronize()
     rt.set_blocking(True)
     okt = torch.tensor([int(ok_all)], device=dev)
