@@ -150,7 +150,33 @@ def main() -> None:
                         "ag_fp8_vs_bf16_max_abs_diff": (ag8.out.float() - ref2.float()).abs().max().item(), "ag_fp8_ok": bool(ok_ag8)})
         ag8.close()
 
-    oks = torch.tensor([int(ok_rs and ok_ag and ok_ag8)], device=dev)
+    # ---------------- GEMM -> reduce-scatter on block-scaled fp8 operands ----------------
+    from roc_shmem_b200.ops.gemm_fp8 import GemmReduceScatterFp8
+    ok_rs8 = True
+    if H % 256 == 0 and K % 128 == 0 and (M // P) % 128 == 0:
+        torch.manual_seed(300 + rank)
+        x8 = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        w8 = (torch.randn(H, K, device=dev) * 0.02).to(torch.bfloat16)
+        qx, qwd = quantize_act(x8), quantize_weight(w8)
+        rs8 = GemmReduceScatterFp8(rt, M, H, K)
+        rs8(qx, qwd)
+        part = gemm_fp8(qx, qwd).float()                          # this rank's bf16-rounded partial, summed in fp32 by NCCL
+        ref_rs8 = torch.empty(M // P, H, device=dev, dtype=torch.float32)
+        dist.reduce_scatter_tensor(ref_rs8, part)
+        torch.cuda.synchronize()
+        rs8.check()
+        diff_rs8 = (rs8.out.float() - ref_rs8).abs().max().item()
+        scale_rs8 = ref_rs8.abs().max().item()
+        ok_rs8 = diff_rs8 <= 1e-2 * scale_rs8 + 1e-3               # one bf16 rounding of the fp32 sum
+        ms_rs8 = timed(lambda: rs8(qx, qwd), args.iters, rt)
+        rs8.check()
+        results.update({"rs_fp8_max_abs_diff": diff_rs8, "rs_fp8_ref_scale": scale_rs8, "rs_fp8_ms_fused": ms_rs8,
+                        "rs_fp8_speedup_vs_bf16_nccl_cublas": results["rs_ms_nccl_cublas"] / ms_rs8,
+                        "rs_fp8_speedup_vs_bf16_fused": results["rs_ms_fused"] / ms_rs8, "rs_fp8_ok": bool(ok_rs8)})
+        rs8.close()
+        del x8, w8, part
+
+    oks = torch.tensor([int(ok_rs and ok_ag and ok_ag8 and ok_rs8)], device=dev)
     dist.all_reduce(oks, op=dist.ReduceOp.MIN)
     results["all_ranks_ok"] = bool(oks.item())
     if rank == 0:

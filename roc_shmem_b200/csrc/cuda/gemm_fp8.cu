@@ -67,6 +67,20 @@ struct Fp8Ag {
   unsigned long long call;
 };
 
+// Reduce-scatter state (GEMM -> reduce-scatter variant): every PE multiplies its K shard, rounds the 128x256 partial
+// tile to bf16 and TMA-stores it into the staging slot [parity][source PE] of the PE that owns those rows, then bumps
+// the tile's signal word there; after its last tile every CTA sums the P partials of the owned tiles dealt to it.
+struct Fp8Rs {
+  int P, my_rank, blocks_per_rank, pad;         // blocks_per_rank: 128-row blocks per owner
+  CUtensorMap map_stage[kMaxPes];               // owner q's slot for (parity, source = this PE): [M/P, N] bf16
+  unsigned long long* sig_remote[kMaxPes];      // owner q's signal words [blocks_per_rank * N/256] (monotonic over calls)
+  const unsigned long long* sig_local;
+  const __nv_bfloat16* stage_local;             // this PE's staging of this call's parity: [P][M/P][N]
+  __nv_bfloat16* out;                           // [M/P, N]
+  int ldo, pad2;
+  unsigned long long call;
+};
+
 struct Fp8Params {
   CoreParams core;             // num_m_blocks counts 128-row blocks
   CUtensorMap map_a, map_b, map_c;
@@ -74,15 +88,27 @@ struct Fp8Params {
   const float* sb;             // [K/128][N/128]
   Fp8Ag ag;                    // used by the all-gather variant only
 };
+struct Fp8RsParams {
+  Fp8Params base;
+  Fp8Rs rs;
+};
+enum : int { F8_PLAIN = 0, F8_AG = 1, F8_RS = 2 };
 
-enum : int { ERR_F8_A_READY = 123, ERR_F8_PEER_READY = 124, ERR_F8_PEER_DONE = 125 };
+enum : int { ERR_F8_A_READY = 123, ERR_F8_PEER_READY = 124, ERR_F8_PEER_DONE = 125, ERR_F8_RS_SIGNAL = 126 };
 
 // Tile order: grouped raster, or (all-gather) source-major starting with this PE's own rows, then the rows of
 // rank me+1, me+2, ... which is also the order in which the pull warps fetch them.
-template <bool kAG>
-__device__ __forceinline__ void f8_tile_coords(const Fp8Params& p, int tile, int* m_blk, int* n_blk) {
-  if constexpr (!kAG) {
+template <int kMode>
+__device__ __forceinline__ void f8_tile_coords(const Fp8Params& p, const Fp8Rs* rs, int tile, int* m_blk, int* n_blk) {
+  if constexpr (kMode == F8_PLAIN) {
     raster_coords(p.core, tile, m_blk, n_blk);
+  } else if constexpr (kMode == F8_RS) {
+    // owner-major, owners visited in the order me+1, me+2, ..., me: the P ranks always write to P different owners
+    const int per_owner = rs->blocks_per_rank * p.core.num_n_blocks;
+    const int step = tile / per_owner, rem = tile - step * per_owner;
+    const int owner = (rs->my_rank + 1 + step) % rs->P;
+    *m_blk = owner * rs->blocks_per_rank + rem % rs->blocks_per_rank;
+    *n_blk = rem / rs->blocks_per_rank;
   } else {
     const int per_src = p.ag.blocks_per_rank * p.core.num_n_blocks;
     const int step = tile / per_src, rem = tile - step * per_src;
@@ -172,8 +198,10 @@ struct FSmem {
   }
 };
 
-template <bool kAG>
-__device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, uint8_t* smem_raw) {
+template <int kMode>
+__device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs* rs, uint8_t* smem_raw) {
+  constexpr bool kAG = kMode == F8_AG;
+  constexpr bool kRS = kMode == F8_RS;
   FSmem L;
   {
     uint32_t r = ptx::smem_u32(smem_raw);
@@ -228,7 +256,7 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, uint8_t* sme
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
-        f8_tile_coords<kAG>(prm, tile, &m_blk, &n_blk);
+        f8_tile_coords<kMode>(prm, rs, tile, &m_blk, &n_blk);
         if constexpr (kAG) {
           if (m_blk / prm.ag.blocks_per_rank != prm.ag.my_rank) {
             if (!wait_ge<false>(prm.ag.arrived + m_blk, (unsigned long long)prm.ag.pieces_per_block * prm.ag.call, g, ERR_F8_A_READY)) break;
@@ -273,11 +301,12 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, uint8_t* sme
     const int ew = warp - 2;               // 0..15
     const int quarter = warp & 3;          // TMEM lanes 32*quarter.. belong to this warp
     const int cg = ew >> 2;                // columns [64*cg, 64*cg + 64) of the tile
+    uint64_t* pend_sig = nullptr;          // reduce-scatter variant: signal word of the tile whose store is in flight
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_blk, n_blk;
-      f8_tile_coords<kAG>(prm, tile, &m_blk, &n_blk);
+      f8_tile_coords<kMode>(prm, rs, tile, &m_blk, &n_blk);
       if constexpr (kAG) {
         // the block's scale columns are pulled like its rows: wait for them before the first scale load
         if (m_blk / prm.ag.blocks_per_rank != prm.ag.my_rank) {
@@ -331,7 +360,20 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, uint8_t* sme
       }
       if (!ok) break;
       // ---- tile output: one 64-column chunk per warp through its swizzled staging buffer ----
-      if (lane == 0) ptx::tma_wait_group_read<0>();
+      if constexpr (kRS) {
+        // the previous tile's store has had a whole tile of promotion work to land: complete it and publish it now
+        if (lane == 0) {
+          ptx::tma_wait_group<0>();
+          if (pend_sig != nullptr) {
+            ptx::fence_proxy_async_all();
+            ptx::fence_acq_rel_sys();
+            ptx::red_release_sys_add_u64(pend_sig, 1);
+            pend_sig = nullptr;
+          }
+        }
+      } else {
+        if (lane == 0) ptx::tma_wait_group_read<0>();
+      }
       __syncwarp();
       const uint32_t rowbase = L.epi(ew) + lane * 128;
 #pragma unroll
@@ -344,18 +386,77 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, uint8_t* sme
       }
       ptx::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        ptx::tma_store_2d(&prm.map_c, L.epi(ew), n_blk * FBN + cg * 64, m_blk * FBM + quarter * 32);
-        ptx::tma_commit_group();
+      if constexpr (!kRS) {
+        if (lane == 0) {
+          ptx::tma_store_2d(&prm.map_c, L.epi(ew), n_blk * FBN + cg * 64, m_blk * FBM + quarter * 32);
+          ptx::tma_commit_group();
+        }
+      } else {
+        if (lane == 0) {
+          // partial chunk -> the owner's staging slot (peer memory), then one signal per warp and tile
+          const int owner = m_blk / rs->blocks_per_rank, m_in = m_blk - owner * rs->blocks_per_rank;
+          ptx::tma_store_2d(&rs->map_stage[owner], L.epi(ew), n_blk * FBN + cg * 64, m_in * FBM + quarter * 32);
+          ptx::tma_commit_group();
+          // the signal (one per warp and tile) is sent once the store is complete: at the next tile's output stage
+          pend_sig = reinterpret_cast<uint64_t*>(rs->sig_remote[owner] + (size_t)m_in * cp.num_n_blocks + n_blk);
+        }
       }
     }
-    if (lane == 0) ptx::tma_wait_group<0>();
+    if (lane == 0) {
+      ptx::tma_wait_group<0>();
+      if constexpr (kRS) {
+        if (pend_sig != nullptr) {
+          ptx::fence_proxy_async_all();
+          ptx::fence_acq_rel_sys();
+          ptx::red_release_sys_add_u64(pend_sig, 1);
+        }
+      }
+    }
     __syncwarp();
   }
 
   // ------------------------------ teardown ---------------------------------------
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (kRS) {
+    // ---- reduce the partials of the tiles this PE owns: owned tile t goes to CTA t % grid ----
+    const int owned = rs->blocks_per_rank * cp.num_n_blocks;
+    const unsigned long long want = (unsigned long long)FEPI_WARPS * rs->P * rs->call;
+    const size_t slot = (size_t)(cp.M / rs->P) * cp.N;           // elements per source slot
+    for (int t = blockIdx.x; t < owned && !*L.abort_flag(); t += gridDim.x) {
+      if (threadIdx.x == 0) wait_ge<true>(rs->sig_local + t, want, g, ERR_F8_RS_SIGNAL);
+      __syncthreads();
+      if (*L.abort_flag()) break;
+      const int m_in = t / cp.num_n_blocks, n_blk = t - m_in * cp.num_n_blocks;
+      // 128 rows x 32 vectors of 8 bf16; the summation order over sources is fixed (0..P-1): reproducible
+      for (int v = threadIdx.x; v < FBM * 32; v += blockDim.x) {
+        const int r = v >> 5, c = (v & 31) * 8;
+        const size_t off = (size_t)(m_in * FBM + r) * cp.N + (size_t)n_blk * FBN + c;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int s0 = 0; s0 < rs->P; s0 += 4) {
+          uint4 x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (s0 + u < rs->P) x[u] = ptx::ld_relaxed_v4(rs->stage_local + (size_t)(s0 + u) * slot + off);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (s0 + u < rs->P) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x[u]);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+            }
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(rs->out + (size_t)(m_in * FBM + r) * rs->ldo + (size_t)n_blk * FBN + c) = o;
+      }
+    }
+    __syncthreads();
+  }
   if constexpr (kAG) {
     // before the kernel ends, CTA 0 makes sure every peer has finished pulling this PE's rows
     if (!*L.abort_flag() && blockIdx.x == 0 && (int)threadIdx.x < prm.ag.P && (int)threadIdx.x != prm.ag.my_rank)
@@ -376,12 +477,17 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, uint8_t* sme
 
 __global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_fp8_blockscale_kernel(const __grid_constant__ Fp8Params prm) {
   extern __shared__ uint8_t smem_raw[];
-  gemm_fp8_body<false>(prm, smem_raw);
+  gemm_fp8_body<F8_PLAIN>(prm, nullptr, smem_raw);
 }
 // all-gather -> GEMM: two more warps per CTA pull the peers' rows and scales while the tensor core runs
 __global__ void __launch_bounds__(FNUM_THREADS + 32 * FPULL_WARPS, 1) ag_gemm_fp8_kernel(const __grid_constant__ Fp8Params prm) {
   extern __shared__ uint8_t smem_raw[];
-  gemm_fp8_body<true>(prm, smem_raw);
+  gemm_fp8_body<F8_AG>(prm, nullptr, smem_raw);
+}
+// GEMM -> reduce-scatter: partial tiles go to their owner's staging over NVLink, owned tiles are reduced at the end
+__global__ void __launch_bounds__(FNUM_THREADS, 1) gemm_rs_fp8_kernel(const __grid_constant__ Fp8RsParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_fp8_body<F8_RS>(prm.base, &prm.rs, smem_raw);
 }
 
 // ---- quantisers ------------------------------------------------------------------------------
@@ -477,6 +583,15 @@ struct AgPlan {
   unsigned int* ticket = nullptr;
 };
 
+struct RsPlan {
+  bshmem_dev_state_t st;
+  int M, N, K, device;
+  unsigned long long call = 0;
+  int* err = nullptr;
+  char* staging_local = nullptr;               // symmetric: [2 parities][P sources][M/P][N] bf16
+  unsigned long long* sig_local = nullptr;     // symmetric: [M/P/128 * N/256]
+};
+
 template <typename T> T* peer_ptr(const bshmem_dev_state_t& st, T* local, int pe) {
   return reinterpret_cast<T*>(st.heap_base[pe] + (reinterpret_cast<char*>(local) - st.heap_base[st.my_pe]));
 }
@@ -493,6 +608,7 @@ int ensure(int dev) {
   BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(gemm_fp8_blockscale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FSMEM_BYTES));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(ag_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FSMEM_BYTES));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(gemm_rs_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FSMEM_BYTES));
   return 0;
 }
 
@@ -635,6 +751,99 @@ int bshmem_fp8_ag_run(void* plan, const void* B8, const float* scale_b, void* C,
   if (ctas > tiles) ctas = tiles;
   ag_gemm_fp8_kernel<<<ctas, FNUM_THREADS + 32 * FPULL_WARPS, FSMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(prm);
   BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// ---- fp8 GEMM -> reduce-scatter ---------------------------------------------------------------------------
+// out[M/P, N] (this PE's rows) = sum over PEs r of dequant(A8_r)[M, K] · dequant(B8_r)[N, K]^T (every PE holds a K shard).
+// Symmetric memory of a plan: staging 2 * M * N bf16 (two call parities) and M/P/128 * N/256 signal words (zeroed,
+// then a barrier before the first call).
+uint64_t bshmem_fp8_rs_staging_bytes(int M, int N) { return 2ull * (uint64_t)M * N * 2; }
+uint64_t bshmem_fp8_rs_signal_bytes(int M, int N, int P) { return (uint64_t)(M / P / FBM) * (N / FBN) * 8; }
+
+int bshmem_fp8_rs_plan(const bshmem_dev_state_t* st, int M, int N, int K, void* staging_local, void* sig_local, void** out) {
+  if (!st || !out) return 1;
+  const int P = st->n_pes;
+  if (P > kMaxPes || M % (P * FBM) || N % FBN || K % FBK) {
+    host::last_error() = "gemm_rs_fp8: needs M % (P*128) == 0, N % 256 == 0, K % 128 == 0";
+    return 1;
+  }
+  if (!in_heap(*st, staging_local, bshmem_fp8_rs_staging_bytes(M, N)) || !in_heap(*st, sig_local, bshmem_fp8_rs_signal_bytes(M, N, P))) {
+    host::last_error() = "gemm_rs_fp8: staging and signal buffers must be symmetric allocations of the stated sizes";
+    return 4;
+  }
+  RsPlan* p = new RsPlan();
+  p->st = *st; p->M = M; p->N = N; p->K = K;
+  p->staging_local = static_cast<char*>(staging_local);
+  p->sig_local = static_cast<unsigned long long*>(sig_local);
+  BSHMEM_CUDA_TRY(cudaGetDevice(&p->device));
+  int rc = ensure(p->device);
+  if (rc) { delete p; return rc; }
+  BSHMEM_CUDA_TRY(cudaMalloc(&p->err, sizeof(int)));
+  BSHMEM_CUDA_TRY(cudaMemset(p->err, 0, sizeof(int)));
+  *out = p;
+  return 0;
+}
+
+// A8: [M, K] e4m3 + scale_a [K/128][M]; B8: [N, K] e4m3 + scale_b [K/128][N/128]; out: [M/P, N] bf16 (ldo).
+int bshmem_fp8_rs_run(void* plan, const void* A8, const float* scale_a, const void* B8, const float* scale_b, void* out, int ldo,
+                      void* stream, int timeout_ms, int max_ctas) {
+  RsPlan* p = static_cast<RsPlan*>(plan);
+  if (!p || ldo % 8) return 1;
+  const int P = p->st.n_pes, me = p->st.my_pe;
+  p->call += 1;
+  const int parity = (int)(p->call & 1);
+  Fp8RsParams prm;
+  memset(&prm, 0, sizeof(prm));
+  Fp8Params& b = prm.base;
+  b.core.M = p->M; b.core.N = p->N; b.core.K = p->K;
+  b.core.num_m_blocks = p->M / FBM; b.core.num_n_blocks = p->N / FBN;
+  b.core.group_m = 32;
+  b.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  b.core.err = p->err;
+  b.sa = scale_a; b.sb = scale_b;
+  int rc = host::make_tmap_2d(&b.map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A8, p->M, p->K, p->K, FBM, FBK);
+  if (rc) return rc;
+  rc = host::make_tmap_2d(&b.map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B8, p->N, p->K, p->K, FBN, FBK);
+  if (rc) return rc;
+  Fp8Rs& r = prm.rs;
+  r.P = P; r.my_rank = me; r.blocks_per_rank = p->M / P / FBM;
+  const uint64_t rows = (uint64_t)p->M / P;
+  const uint64_t slot_bytes = rows * p->N * 2;
+  for (int q = 0; q < P; ++q) {
+    char* slot = peer_ptr(p->st, p->staging_local, q) + ((uint64_t)parity * P + me) * slot_bytes;
+    rc = host::make_tmap_2d(&r.map_stage[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, slot, rows, p->N, p->N, 32, 64);
+    if (rc) return rc;
+    r.sig_remote[q] = peer_ptr(p->st, p->sig_local, q);
+  }
+  r.sig_local = p->sig_local;
+  r.stage_local = reinterpret_cast<const __nv_bfloat16*>(p->staging_local + (uint64_t)parity * P * slot_bytes);
+  r.out = static_cast<__nv_bfloat16*>(out);
+  r.ldo = ldo;
+  r.call = p->call;
+  int ctas = g_sms[p->device];
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  const int tiles = b.core.num_m_blocks * b.core.num_n_blocks;
+  if (ctas > tiles) ctas = tiles;
+  gemm_rs_fp8_kernel<<<ctas, FNUM_THREADS, FSMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(prm);
+  BSHMEM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int bshmem_fp8_rs_error_site(void* plan, int clear) {
+  RsPlan* p = static_cast<RsPlan*>(plan);
+  int v = 0;
+  if (!p || !p->err) return 0;
+  cudaMemcpy(&v, p->err, sizeof(int), cudaMemcpyDeviceToHost);
+  if (clear && v) cudaMemset(p->err, 0, sizeof(int));
+  return v;
+}
+
+int bshmem_fp8_rs_destroy(void* plan) {
+  RsPlan* p = static_cast<RsPlan*>(plan);
+  if (!p) return 0;
+  cudaFree(p->err);
+  delete p;
   return 0;
 }
 

@@ -186,3 +186,65 @@ class AllGatherGemmFp8:
         if self.plan:
             self.lib.bshmem_fp8_ag_destroy(self.plan)
             self.plan = None
+
+
+class GemmReduceScatterFp8:
+    """out[M/P, N] (this PE's rows, bf16) = sum over PEs r of dequant(a_r)[M, K] @ dequant(b_r)[N, K].T in ONE kernel:
+    the block-scaled fp8 GEMM whose epilogue TMA-stores its bf16 partial tiles into the owner PE's staging over NVLink
+    and signals per tile; after its last tile every CTA sums the P partials of the owned tiles dealt to it (fixed
+    order, reproducible).  Staging is double-buffered by call parity and signals are monotonic, so back-to-back calls
+    need no barrier."""
+
+    algorithm = ("one kernel: block-scaled fp8 tcgen05 GEMM (128x256 tiles) whose epilogue TMA-stores bf16 partial tiles into "
+                 "the owner PE's staging over NVLink + per-tile signal; CTAs then reduce the P partials of the owned tiles")
+
+    def __init__(self, rt, M: int, N: int, K: int, timeout_ms: int = 2000, max_ctas: int = 0):
+        self.rt, self.M, self.N, self.K = rt, M, N, K
+        self.lib = fp8_lib()
+        lib, VP, I = self.lib, C.c_void_p, C.c_int
+        if not getattr(lib, "_rs_declared", False):
+            lib.bshmem_fp8_rs_staging_bytes.restype = C.c_uint64
+            lib.bshmem_fp8_rs_staging_bytes.argtypes = [I, I]
+            lib.bshmem_fp8_rs_signal_bytes.restype = C.c_uint64
+            lib.bshmem_fp8_rs_signal_bytes.argtypes = [I, I, I]
+            lib.bshmem_fp8_rs_plan.restype = I
+            lib.bshmem_fp8_rs_plan.argtypes = [VP, I, I, I, VP, VP, C.POINTER(VP)]
+            lib.bshmem_fp8_rs_run.restype = I
+            lib.bshmem_fp8_rs_run.argtypes = [VP, VP, VP, VP, VP, VP, I, VP, I, I]
+            lib.bshmem_fp8_rs_error_site.restype = I
+            lib.bshmem_fp8_rs_error_site.argtypes = [VP, I]
+            lib.bshmem_fp8_rs_destroy.restype = I
+            lib.bshmem_fp8_rs_destroy.argtypes = [VP]
+            lib._rs_declared = True
+        P = rt.n_pes
+        self.timeout_ms, self.max_ctas = timeout_ms, max_ctas
+        self.staging = rt.empty((lib.bshmem_fp8_rs_staging_bytes(M, N),), torch.uint8, align=1024)
+        self.signals = rt.zeros((max(1, lib.bshmem_fp8_rs_signal_bytes(M, N, P) // 8),), torch.int64)
+        self.out = torch.empty((M // P, N), dtype=torch.bfloat16, device=rt.device)
+        st = rt.device_state()
+        plan = C.c_void_p()
+        rc = lib.bshmem_fp8_rs_plan(C.byref(st), M, N, K, self.staging.data_ptr(), self.signals.data_ptr(), C.byref(plan))
+        if rc != 0:
+            raise RuntimeError(f"gemm_rs_fp8 plan failed ({rc}): {lib.bshmem_fp8_last_error().decode()}")
+        self.plan = plan
+        rt.barrier_all()      # every PE's signal words are zero before anyone sends
+
+    def __call__(self, a: Fp8Tensor, b: Fp8Tensor, out: Optional[torch.Tensor] = None) -> int:
+        if a.kind != "act" or b.kind != "weight" or a.q.shape != (self.M, self.K) or b.q.shape != (self.N, self.K):
+            raise ValueError("gemm_rs_fp8 takes (activation [M, K], weight [N, K]) of the planned shape")
+        out = self.out if out is None else out
+        rc = self.lib.bshmem_fp8_rs_run(self.plan, a.q.data_ptr(), a.scales.data_ptr(), b.q.data_ptr(), b.scales.data_ptr(),
+                                        out.data_ptr(), out.stride(0), _stream(), self.timeout_ms, self.max_ctas)
+        if rc != 0:
+            raise RuntimeError(f"gemm_rs_fp8 run failed ({rc}): {self.lib.bshmem_fp8_last_error().decode()}")
+        return 1
+
+    def check(self) -> None:
+        site = self.lib.bshmem_fp8_rs_error_site(self.plan, 1)
+        if site:
+            raise RuntimeError(f"gemm_rs_fp8: a bounded in-kernel wait ran out (site {site})")
+
+    def close(self) -> None:
+        if self.plan:
+            self.lib.bshmem_fp8_rs_destroy(self.plan)
+            self.plan = None

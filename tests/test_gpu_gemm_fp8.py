@@ -80,3 +80,27 @@ def test_all_gather_gemm_fp8_single_pe_equals_plain_kernel():
         op.close()
     finally:
         shmem.finalize()
+
+
+def test_gemm_reduce_scatter_fp8_single_pe_equals_plain_kernel():
+    """One PE: the partial tiles go through the staging slot and the in-kernel reduction of a single partial;
+    the result must equal the plain fp8 GEMM bit for bit, on both call parities."""
+    import roc_shmem_b200 as shmem
+    from roc_shmem_b200.ops.gemm_fp8 import GemmReduceScatterFp8, gemm_fp8, quantize_act, quantize_weight
+    rt = shmem.init("device", rank=0, world_size=1, heap_bytes=256 << 20, timeout_ms=5000)
+    try:
+        torch.manual_seed(6)
+        M, N, K = 640, 512, 384
+        qa = quantize_act(torch.randn(M, K, device="cuda").to(torch.bfloat16))
+        qw = quantize_weight((torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16))
+        op = GemmReduceScatterFp8(rt, M, N, K)
+        ref = gemm_fp8(qa, qw)
+        for _ in range(3):
+            op.out.fill_(7.0)
+            op(qa, qw)
+            torch.cuda.synchronize()
+            op.check()
+            assert torch.equal(op.out, ref)
+        op.close()
+    finally:
+        shmem.finalize()
