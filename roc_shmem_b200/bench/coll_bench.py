@@ -35,12 +35,47 @@ def timed(fn, iters, rt):
     return float(t.item())
 
 
+def timed_graph(fn, iters, rt):
+    """Same loop captured once in a CUDA graph and replayed: device time without the per-call host cost."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        rt.set_stream(side)                      # the runtime enqueues where it is told to
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    rt.set_stream(torch.cuda.current_stream())
+    rt.barrier_all()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        rt.set_stream(torch.cuda.current_stream())   # the capturing stream
+        for _ in range(iters):
+            fn()
+    rt.set_stream(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    rt.barrier_all()
+    g.replay()                                   # warm-up replay
+    torch.cuda.synchronize()
+    rt.barrier_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--out", default="")
     ap.add_argument("--ctas", type=int, default=128)
     ap.add_argument("--nvls", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="also time barrier and small allreduces replayed from a CUDA graph")
     ap.add_argument("--team-sizes", default="", help="comma list: also time allreduce / fcollect on disjoint teams of that many PEs")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -145,6 +180,24 @@ def main() -> None:
         us_n = timed(lambda: dist.all_to_all_single(ref, a_src), iters, rt)
         rows.append({"op": "alltoall", "bytes": blk * P, "us": us, "nccl_us": us_n, "busbw_GBps": (P - 1) * blk / us / 1e3,
                      "ok": bool(good)})
+    # ---- launch-bound sizes replayed from a CUDA graph (the runtime follows the capturing stream) ----
+    if args.graph:
+        us = timed_graph(lambda: rt.barrier_all(), 50, rt)
+        one = torch.zeros(1, device=dev)
+        us_n = timed_graph(lambda: dist.all_reduce(one), 20, rt)   # dist.barrier() cannot be captured: a 4-byte all_reduce stands in
+        rows.append({"op": "barrier_graph", "bytes": 0, "us": us, "nccl_us": us_n})
+        for nbytes in (1024, 16384, 65536, 262144, 1 << 20):
+            if nbytes > args.max_bytes:
+                continue
+            n = nbytes // 4
+            n -= n % P
+            src = src_all[: n * 4].view(torch.float32)
+            dst = dst_all[: n * 4].view(torch.float32)
+            src.copy_(torch.randn(n, device=dev))
+            ref = src.clone()
+            us = timed_graph(lambda: rt.reduce(dst, src, "sum"), 20, rt)
+            us_n = timed_graph(lambda: dist.all_reduce(ref), 20, rt)
+            rows.append({"op": "allreduce_sum_graph", "dtype": "float32", "bytes": n * 4, "us": us, "nccl_us": us_n})
     # ---- sub-teams: all teams of a size run their collective at the same time (team k = PEs [k*ts, (k+1)*ts)) ----
     for ts in [int(v) for v in args.team_sizes.split(",") if v]:
         if ts < 2 or ts >= P or P % ts:

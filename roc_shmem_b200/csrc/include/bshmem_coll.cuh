@@ -274,10 +274,94 @@ __device__ __forceinline__ void split_range(size_t n, int parts, int idx, size_t
 
 constexpr size_t kOneShotBytes = 64 * 1024;   // below this every PE reduces the whole vector itself
 
+static_assert(BSHMEM_OFF_SCRATCH + BSHMEM_SCRATCH_BYTES <= BSHMEM_OFF_LL && BSHMEM_OFF_LL + BSHMEM_LL_BYTES <= BSHMEM_OFF_SLAB,
+              "internal heap regions overlap");
+
+// Low-latency allreduce for small vectors on the world team, single block: ONE NVLink exchange instead of
+// sync + reduce + barrier.  Every PE pushes its vector into a per-sender slot on every PE as 8-byte words that carry
+// 4 bytes of data and the 32-bit epoch, so data and "it has arrived" travel in the same store; receivers poll the
+// words, reduce in team order (identical result on every PE) and return.  The source is reusable on return (it was
+// copied out); slots alternate by epoch parity: a sender can only write epoch e+2 after it finished e+1, which needed
+// this PE's data of e+1, which this PE sent after it had read every slot of e.
+template <typename T>
+__device__ __forceinline__ int team_reduce_ll(const State& s, const Team& t, int op, T* dest, const T* source, size_t n) {
+  using A = typename Acc<T>::type;
+  constexpr int kUnit = sizeof(T) > 4 ? (int)sizeof(T) : 4;        // bytes reduced together: whole elements
+  constexpr int kWords = kUnit / 4, kElems = kUnit / (int)sizeof(T);
+  __shared__ unsigned long long ll_epoch;
+  __shared__ int ll_status;
+  char* my_base = s.heap_base[s.my_pe] + BSHMEM_OFF_LL;
+  if (threadIdx.x == 0) {
+    ll_epoch = *reinterpret_cast<unsigned long long*>(my_base) + 1;
+    ll_status = BSHMEM_OK;
+  }
+  __syncthreads();
+  const unsigned long long e = ll_epoch;
+  const unsigned long long flag = (e & 0xFFFFFFFFull) << 32;
+  const int nwords = (int)(n * sizeof(T) / 4);
+  const size_t slot0 = 64 + (size_t)(e & 1) * BSHMEM_MAX_PES * BSHMEM_LL_SLOT_BYTES;
+  // ---- push: my words into slot [my_idx] of every member (myself included) ----
+  const uint32_t* src32 = reinterpret_cast<const uint32_t*>(source);
+  for (int w = threadIdx.x; w < nwords; w += blockDim.x) {
+    const unsigned long long packed = flag | src32[w];
+    for (int k = 0; k < t.size; ++k) {
+      char* peer = s.heap_base[dev::team_pe(t, k)] + BSHMEM_OFF_LL + slot0 + (size_t)t.my_idx * BSHMEM_LL_SLOT_BYTES;
+      asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(peer + (size_t)w * 8), "l"(packed) : "memory");
+    }
+  }
+  // ---- receive + reduce: unit u = kWords consecutive words of every sender ----
+  const int nunits = nwords / kWords;
+  const unsigned long long t0 = dev::timer();
+  for (int u = threadIdx.x; u < nunits; u += blockDim.x) {
+    A acc[kElems];
+    for (int k = 0; k < t.size; ++k) {
+      const char* slot = my_base + slot0 + (size_t)k * BSHMEM_LL_SLOT_BYTES + (size_t)u * kWords * 8;
+      uint32_t raw[kWords];
+#pragma unroll
+      for (int w = 0; w < kWords; ++w) {
+        unsigned long long v;
+        unsigned it = 0;
+        while (true) {
+          asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(slot + w * 8) : "memory");
+          if ((v >> 32) == (e & 0xFFFFFFFFull)) break;
+          if ((++it & 63) == 0 && dev::timer() - t0 > s.timeout_ns) {
+            dev::record_error(s, BSHMEM_ERR_TIMEOUT, dev::team_pe(t, k), BSHMEM_WHERE_BARRIER, (uint64_t)slot, e, v >> 32);
+            ll_status = BSHMEM_ERR_TIMEOUT;
+            break;
+          }
+        }
+        raw[w] = (uint32_t)v;
+      }
+      T vals[kElems];
+      memcpy(vals, raw, kUnit);
+#pragma unroll
+      for (int i = 0; i < kElems; ++i) acc[i] = k == 0 ? to_acc<T>(vals[i]) : apply<A>(op, acc[i], to_acc<T>(vals[i]));
+    }
+    T out[kElems];
+#pragma unroll
+    for (int i = 0; i < kElems; ++i) out[i] = from_acc<T>(acc[i]);
+    memcpy(reinterpret_cast<char*>(dest) + (size_t)u * kUnit, out, kUnit);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *reinterpret_cast<unsigned long long*>(my_base) = e;
+    dev::stat(s, BSHMEM_DSTAT_COLL);
+    dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, n * sizeof(T));
+  }
+  const int rc = ll_status;
+  __syncthreads();
+  return rc;
+}
+
 // allreduce (`*_to_all`): dest and source are symmetric; dest may alias source.
 template <typename T>
 __device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
                                            int cta = 0, int ncta = 1) {
+  // small vectors on the world team: one exchange (the condition is the same on every PE: symmetric addresses)
+  if (t.slot == 0 && t.size == s.n_pes && ncta == 1 && n * sizeof(T) <= BSHMEM_LL_PAYLOAD_BYTES && (n * sizeof(T)) % 4 == 0 &&
+      n * sizeof(T) >= (sizeof(T) > 4 ? sizeof(T) : 4) &&
+      ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & (sizeof(T) > 4 ? 7 : 3)) == 0)
+    return team_reduce_ll<T>(s, t, op, dest, source, n);
   const T* srcs[BSHMEM_MAX_PES];
   T* dsts[BSHMEM_MAX_PES];
   for (int k = 0; k < t.size; ++k) {

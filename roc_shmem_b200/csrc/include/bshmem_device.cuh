@@ -35,6 +35,12 @@
 #define BSHMEM_XCHG_BYTES ((uint64_t)BSHMEM_MAX_TEAMS * BSHMEM_MAX_PES * 8)
 #define BSHMEM_OFF_SCRATCH (BSHMEM_OFF_XCHG + BSHMEM_XCHG_BYTES)   /* 64 KiB bounce area (host p/g/AMO)      */
 #define BSHMEM_SCRATCH_BYTES (64ull << 10)
+/* Low-latency allreduce slots at 1 MiB: a local epoch word, then [2 parities][sender PE][payload words of 8 bytes =
+ * 4 bytes of data + the 32-bit epoch], written by peers with single 8-byte stores (data and flag arrive together).   */
+#define BSHMEM_OFF_LL (1ull << 20)
+#define BSHMEM_LL_PAYLOAD_BYTES 4096ull
+#define BSHMEM_LL_SLOT_BYTES (2 * BSHMEM_LL_PAYLOAD_BYTES)
+#define BSHMEM_LL_BYTES (64 + 2ull * BSHMEM_MAX_PES * BSHMEM_LL_SLOT_BYTES)
 #define BSHMEM_OFF_SLAB (2ull << 20)                              /* device-callable slab allocator region   */
 #define BSHMEM_SLAB_BYTES (2ull << 20)
 

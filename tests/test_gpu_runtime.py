@@ -269,3 +269,30 @@ def test_device_timeline_records_puts_and_waits(rt):
     assert len(ev) == 8 and [e["seq"] for e in ev] == list(range(10, 18))
     rt.trace_enable(0)
     rt.free(sym)
+
+
+@pytest.mark.parametrize("dtype,n,op", [(torch.float32, 1000, 0), (torch.float32, 1, 2), (torch.bfloat16, 2048, 0),
+                                        (torch.int64, 512, 0), (torch.int32, 77, 1), (torch.float64, 33, 3)])
+def test_group_allreduce_low_latency_path(group, dtype, n, op):
+    """Vectors of at most 4 KiB on the world team with one block take the one-exchange path (data and epoch in the
+    same 8-byte store); repeated calls alternate the slot parity, the last call reduces in place."""
+    from roc_shmem_b200 import gpu
+    srcs = group.empty((n,), dtype)
+    dsts = group.empty((n,), dtype)
+    torch.manual_seed(n)
+    for rep in range(5):
+        for s in srcs:
+            if dtype.is_floating_point:
+                s.copy_((torch.rand(n, device="cuda") + 0.5).to(dtype))
+            else:
+                s.copy_(torch.randint(1, 5, (n,), device="cuda", dtype=dtype))
+        wide = torch.float64 if dtype.is_floating_point else torch.int64
+        st = torch.stack([s.to(wide) for s in srcs])
+        ref = (st.sum(0) if op == 0 else st.min(0).values if op == 1 else st.max(0).values if op == 2 else st.prod(0))
+        in_place = rep == 4
+        group.collective(gpu.COLL_REDUCE, srcs if in_place else dsts, srcs, n, dtype=dtype, op=op, ctas=1)
+        for d in (srcs if in_place else dsts):
+            if dtype.is_floating_point:
+                assert torch.allclose(d.to(wide), ref, rtol=2e-2 if dtype == torch.bfloat16 else 1e-6), (rep, dtype)
+            else:
+                assert torch.equal(d.to(wide), ref), (rep, dtype)
