@@ -133,6 +133,7 @@ struct CollArgs {
   uint64_t dst_off, src_off, n;   // n: elements for reductions, bytes otherwise
   uint64_t psync_off;  // active set
   int use_nvls;
+  unsigned long long ll_epoch;   // != 0: epoch of a host-launched low-latency allreduce (same on every PE)
 };
 
 template <typename T>
@@ -146,7 +147,7 @@ __device__ int reduce_typed(const State& s, const DTeam& t, const CollArgs& a, i
         (a.n * sizeof(T)) % 16 == 0)
       return coll::team_reduce_nvls<T>(s, t, d, src, a.n, cta, ncta);
   }
-  return coll::team_reduce<T>(s, t, a.op, d, src, a.n, cta, ncta);
+  return coll::team_reduce<T>(s, t, a.op, d, src, a.n, cta, ncta, a.ll_epoch);
 }
 
 __device__ int run_coll(const State& s, DTeam t, const CollArgs& a, int cta, int ncta) {
@@ -391,6 +392,18 @@ class GpuBackend final : public Backend {
       ctas = (int)((bytes + (32u << 10) - 1) / (32u << 10));
       if (ctas > coll_ctas_) ctas = coll_ctas_;
     }
+    a.ll_epoch = 0;
+    const uint64_t unit = bshmem_dtype_size(a.dtype) > 4 ? bshmem_dtype_size(a.dtype) : 4;
+    if (a.kind == BSHMEM_COLL_REDUCE && g.slot == 0 && g.set.size == heap_->n_pes && !use_nvls_ &&
+        bytes > BSHMEM_LL_PAYLOAD_BYTES && bytes <= BSHMEM_LLB_PAYLOAD_BYTES && bytes % unit == 0 &&
+        ((a.dst_off | a.src_off) & (unit - 1)) == 0) {
+      // mid-size allreduce on the world team: one exchange through the per-sender slots.  The conditions are exactly
+      // those under which the kernel takes that path, and every PE makes the same sequence of such calls, so this
+      // counter is the same everywhere and its parity alternates between consecutive uses of the slots.
+      a.ll_epoch = ++ll_epoch_;
+      ctas = (int)((bytes + (8u << 10) - 1) / (8u << 10));      // 8 KiB of payload per block
+      if (ctas > coll_ctas_) ctas = coll_ctas_;
+    }
     k_coll<<<ctas, 512, 0, stream_>>>(state_, team_of(g), a, dstatus_);
     RT_TRY(cudaGetLastError());
     if (!blocking_) return BSHMEM_OK;
@@ -479,6 +492,7 @@ class GpuBackend final : public Backend {
   bool blocking_ = true;
   bool use_nvls_ = false;
   int coll_ctas_ = 32;
+  unsigned long long ll_epoch_ = 0;     // epochs of host-launched low-latency allreduces
   std::string err_;
 };
 

@@ -274,7 +274,8 @@ __device__ __forceinline__ void split_range(size_t n, int parts, int idx, size_t
 
 constexpr size_t kOneShotBytes = 64 * 1024;   // below this every PE reduces the whole vector itself
 
-static_assert(BSHMEM_OFF_SCRATCH + BSHMEM_SCRATCH_BYTES <= BSHMEM_OFF_LL && BSHMEM_OFF_LL + BSHMEM_LL_BYTES <= BSHMEM_OFF_SLAB,
+static_assert(BSHMEM_OFF_SCRATCH + BSHMEM_SCRATCH_BYTES <= BSHMEM_OFF_LL && BSHMEM_OFF_LL + BSHMEM_LL_BYTES <= BSHMEM_OFF_SLAB &&
+              BSHMEM_OFF_SLAB + BSHMEM_SLAB_BYTES <= BSHMEM_OFF_LLB && BSHMEM_OFF_LLB + BSHMEM_LLB_BYTES <= BSHMEM_INTERNAL_BYTES,
               "internal heap regions overlap");
 
 // Low-latency allreduce for small vectors on the world team, single block: ONE NVLink exchange instead of
@@ -283,39 +284,48 @@ static_assert(BSHMEM_OFF_SCRATCH + BSHMEM_SCRATCH_BYTES <= BSHMEM_OFF_LL && BSHM
 // words, reduce in team order (identical result on every PE) and return.  The source is reusable on return (it was
 // copied out); slots alternate by epoch parity: a sender can only write epoch e+2 after it finished e+1, which needed
 // this PE's data of e+1, which this PE sent after it had read every slot of e.
+// `epoch_in` = 0: single block, the epoch is a counter in this PE's heap (any caller, device-initiated included);
+// otherwise the host supplies the epoch of a multi-block launch (block `cta` of `ncta` takes a share of the words)
+// and the larger slot region is used.
 template <typename T>
-__device__ __forceinline__ int team_reduce_ll(const State& s, const Team& t, int op, T* dest, const T* source, size_t n) {
+__device__ __forceinline__ int team_reduce_ll(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
+                                              unsigned long long epoch_in = 0, int cta = 0, int ncta = 1) {
   using A = typename Acc<T>::type;
   constexpr int kUnit = sizeof(T) > 4 ? (int)sizeof(T) : 4;        // bytes reduced together: whole elements
   constexpr int kWords = kUnit / 4, kElems = kUnit / (int)sizeof(T);
   __shared__ unsigned long long ll_epoch;
   __shared__ int ll_status;
-  char* my_base = s.heap_base[s.my_pe] + BSHMEM_OFF_LL;
+  const size_t region = epoch_in ? BSHMEM_OFF_LLB : BSHMEM_OFF_LL;
+  const size_t slot_bytes = epoch_in ? BSHMEM_LLB_SLOT_BYTES : BSHMEM_LL_SLOT_BYTES;
+  char* my_base = s.heap_base[s.my_pe] + region;
   if (threadIdx.x == 0) {
-    ll_epoch = *reinterpret_cast<unsigned long long*>(my_base) + 1;
+    ll_epoch = epoch_in ? epoch_in : *reinterpret_cast<unsigned long long*>(my_base) + 1;
     ll_status = BSHMEM_OK;
   }
   __syncthreads();
   const unsigned long long e = ll_epoch;
   const unsigned long long flag = (e & 0xFFFFFFFFull) << 32;
   const int nwords = (int)(n * sizeof(T) / 4);
-  const size_t slot0 = 64 + (size_t)(e & 1) * BSHMEM_MAX_PES * BSHMEM_LL_SLOT_BYTES;
+  const size_t slot0 = (epoch_in ? 0 : 64) + (size_t)(e & 1) * BSHMEM_MAX_PES * slot_bytes;
+  // this block's share, in whole units
+  const int units_all = nwords / kWords;
+  const int per = (units_all + ncta - 1) / ncta;
+  const int u_begin = min(per * cta, units_all), u_end = min(u_begin + per, units_all);
   // ---- push: my words into slot [my_idx] of every member (myself included) ----
   const uint32_t* src32 = reinterpret_cast<const uint32_t*>(source);
-  for (int w = threadIdx.x; w < nwords; w += blockDim.x) {
+  for (int w = u_begin * kWords + threadIdx.x; w < u_end * kWords; w += blockDim.x) {
     const unsigned long long packed = flag | src32[w];
     for (int k = 0; k < t.size; ++k) {
-      char* peer = s.heap_base[dev::team_pe(t, k)] + BSHMEM_OFF_LL + slot0 + (size_t)t.my_idx * BSHMEM_LL_SLOT_BYTES;
+      char* peer = s.heap_base[dev::team_pe(t, k)] + region + slot0 + (size_t)t.my_idx * slot_bytes;
       asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(peer + (size_t)w * 8), "l"(packed) : "memory");
     }
   }
   // ---- receive + reduce: unit u = kWords consecutive words of every sender ----
-  const int nunits = nwords / kWords;
   const unsigned long long t0 = dev::timer();
-  for (int u = threadIdx.x; u < nunits; u += blockDim.x) {
+  for (int u = u_begin + threadIdx.x; u < u_end; u += blockDim.x) {
     A acc[kElems];
     for (int k = 0; k < t.size; ++k) {
-      const char* slot = my_base + slot0 + (size_t)k * BSHMEM_LL_SLOT_BYTES + (size_t)u * kWords * 8;
+      const char* slot = my_base + slot0 + (size_t)k * slot_bytes + (size_t)u * kWords * 8;
       uint32_t raw[kWords];
 #pragma unroll
       for (int w = 0; w < kWords; ++w) {
@@ -344,9 +354,11 @@ __device__ __forceinline__ int team_reduce_ll(const State& s, const Team& t, int
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    *reinterpret_cast<unsigned long long*>(my_base) = e;
-    dev::stat(s, BSHMEM_DSTAT_COLL);
-    dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, n * sizeof(T));
+    if (!epoch_in) *reinterpret_cast<unsigned long long*>(my_base) = e;
+    if (cta == 0) {
+      dev::stat(s, BSHMEM_DSTAT_COLL);
+      dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, n * sizeof(T));
+    }
   }
   const int rc = ll_status;
   __syncthreads();
@@ -356,12 +368,13 @@ __device__ __forceinline__ int team_reduce_ll(const State& s, const Team& t, int
 // allreduce (`*_to_all`): dest and source are symmetric; dest may alias source.
 template <typename T>
 __device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
-                                           int cta = 0, int ncta = 1) {
+                                           int cta = 0, int ncta = 1, unsigned long long ll_epoch = 0) {
   // small vectors on the world team: one exchange (the condition is the same on every PE: symmetric addresses)
-  if (t.slot == 0 && t.size == s.n_pes && ncta == 1 && n * sizeof(T) <= BSHMEM_LL_PAYLOAD_BYTES && (n * sizeof(T)) % 4 == 0 &&
-      n * sizeof(T) >= (sizeof(T) > 4 ? sizeof(T) : 4) &&
-      ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & (sizeof(T) > 4 ? 7 : 3)) == 0)
-    return team_reduce_ll<T>(s, t, op, dest, source, n);
+  if (t.slot == 0 && t.size == s.n_pes && (n * sizeof(T)) % (sizeof(T) > 4 ? sizeof(T) : 4) == 0 && n > 0 &&
+      ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & (sizeof(T) > 4 ? 7 : 3)) == 0) {
+    if (ncta == 1 && n * sizeof(T) <= BSHMEM_LL_PAYLOAD_BYTES) return team_reduce_ll<T>(s, t, op, dest, source, n);
+    if (ll_epoch != 0 && n * sizeof(T) <= BSHMEM_LLB_PAYLOAD_BYTES) return team_reduce_ll<T>(s, t, op, dest, source, n, ll_epoch, cta, ncta);
+  }
   const T* srcs[BSHMEM_MAX_PES];
   T* dsts[BSHMEM_MAX_PES];
   for (int k = 0; k < t.size; ++k) {

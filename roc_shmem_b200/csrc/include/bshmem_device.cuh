@@ -26,7 +26,13 @@
 #include "bshmem_types.h"
 
 // ---- layout of the runtime-internal region at the start of every heap ----------
-#define BSHMEM_INTERNAL_BYTES (4ull << 20)
+#define BSHMEM_INTERNAL_BYTES (40ull << 20)
+/* Low-latency allreduce slots for host-launched, multi-block calls (epoch supplied by the host): 4 MiB .. 36 MiB,
+ * [2 parities][sender PE][512 KiB of payload as 8-byte words].                                                    */
+#define BSHMEM_OFF_LLB (4ull << 20)
+#define BSHMEM_LLB_PAYLOAD_BYTES (512ull << 10)
+#define BSHMEM_LLB_SLOT_BYTES (2 * BSHMEM_LLB_PAYLOAD_BYTES)
+#define BSHMEM_LLB_BYTES (2ull * BSHMEM_MAX_PES * BSHMEM_LLB_SLOT_BYTES)
 #define BSHMEM_OFF_FLAGS 0ull                                   /* [team][cta][pe] u64, written by peers   */
 #define BSHMEM_FLAGS_BYTES ((uint64_t)BSHMEM_MAX_TEAMS * BSHMEM_MAX_COLL_CTAS * BSHMEM_MAX_PES * 8)
 #define BSHMEM_OFF_EPOCHS (BSHMEM_OFF_FLAGS + BSHMEM_FLAGS_BYTES) /* [team][cta] u64, local only           */
