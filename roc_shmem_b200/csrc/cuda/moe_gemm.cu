@@ -12,6 +12,8 @@
 //   optional wait on the dispatch arrival words before the first A load.
 // There is no grouped GEMM in the reference; the layout conventions are those of
 // moe_kernels.cu.
+#include <cstdlib>
+
 #include "gemm_core.cuh"
 #include "moe_common.h"
 #include "tma_host.h"
@@ -30,6 +32,7 @@ struct GroupedParams {
   int a_blocks_per_group;          // 256-row blocks between consecutive groups in A and C
   int b_rows_per_group;            // rows between consecutive groups in B
   int k_rows_per_group;            // token rows between consecutive groups of A and B (transposed-operand mode)
+  int tn3d;                        // transposed-operand mode: maps are 3-D column-block views, one copy per operand
   int group_m;
   int P;                           // arrival wait: number of words, 0 = no wait
   const unsigned long long* arrive;
@@ -111,6 +114,11 @@ struct GroupedTN : Grouped<false> {
     const int g = m_blk / p.a_blocks_per_group;
     const int tok = g * p.k_rows_per_group + k_elem;
     const int m0 = (m_blk - g * p.a_blocks_per_group) * BM, n0 = n_blk * BN;
+    if (p.tn3d) {                  // one 32 KiB copy per operand: {64, 64 tokens, 4 column blocks}
+      ptx::tma_load_3d(a_smem, ma, bar, 0, tok, m0 / 64);
+      ptx::tma_load_3d(b_smem, mb, bar, 0, tok, n0 / 64);
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       ptx::tma_load_2d(a_smem + i * kBlock, ma, bar, m0 + i * 64, tok);
@@ -237,11 +245,19 @@ int bshmem_moe_grouped_gemm_tn(const void* A, const void* B, void* C, int G, int
   p.a_blocks_per_group = M / BM;
   p.k_rows_per_group = cap;
   p.group_m = 16;
-  // boxes of 64 MN-elements (128 bytes, the swizzle span) by 64 tokens
-  rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)G * cap, M, lda, 64, 64);
-  if (rc) return rc;
-  rc = host::make_tmap_2d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, (uint64_t)G * cap, N, ldb, 64, 64);
-  if (rc) return rc;
+  // preferred: one 3-D copy per operand and stage; if the driver refuses that view, boxes of 64 MN-elements
+  // (128 bytes, the swizzle span) by 64 tokens, four per operand and stage
+  static const bool no3d = getenv("B200SHMEM_TN_2D") != nullptr;
+  p.tn3d = 0;
+  if (!no3d && host::make_tmap_colblocks_3d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, (uint64_t)G * cap, M, lda, 64, 4) == 0 &&
+      host::make_tmap_colblocks_3d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, (uint64_t)G * cap, N, ldb, 64, 4) == 0)
+    p.tn3d = 1;
+  if (!p.tn3d) {
+    rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)G * cap, M, lda, 64, 64);
+    if (rc) return rc;
+    rc = host::make_tmap_2d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, (uint64_t)G * cap, N, ldb, 64, 64);
+    if (rc) return rc;
+  }
   rc = host::make_tmap_2d(&p.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, (uint64_t)G * M, N, ldc, 32, EPI_COLS);
   if (rc) return rc;
   int ctas = g_sms[dev];

@@ -66,5 +66,30 @@ inline int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes
   return 0;
 }
 
+// 3-D view of a row-major [rows, cols] 2-byte tensor for MN-major operands: dim0 = 64 elements inside a 64-wide
+// column block, dim1 = rows, dim2 = column block (128 bytes apart).  One box {64, box_rows, box_blocks} lands in
+// shared memory as box_blocks consecutive [box_rows][64] blocks with the 128-byte swizzle, i.e. what several 2-D
+// {64, box_rows} boxes would write, in one copy.  Returns non-zero if the driver refuses the (non-monotonic) strides.
+inline int make_tmap_colblocks_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t cols,
+                                  uint64_t ld, uint32_t box_rows, uint32_t box_blocks) {
+  auto fn = encode_fn();
+  if (!fn) { last_error() = "cuTensorMapEncodeTiled entry point not available"; return 7; }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15) || cols % 64) {
+    last_error() = "TMA needs a 16-byte aligned base and row pitch, and a column count that is a multiple of 64";
+    return 1;
+  }
+  cuuint64_t dims[3] = {64, rows, cols / 64};
+  cuuint64_t strides[2] = {ld * 2, 128};
+  cuuint32_t box[3] = {64, box_rows, box_blocks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    last_error() = "cuTensorMapEncodeTiled (3-D column blocks) failed with CUresult " + std::to_string((int)r);
+    return 7;
+  }
+  return 0;
+}
+
 }  // namespace host
 }  // namespace bshmem
