@@ -126,3 +126,13 @@ __all__ = ["init", "finalize", "global_exit", "current", "set_current", "Config"
            "ShmemError", "ShmemTimeout", "ShmemAborted", "TEAM_WORLD", "TEAM_INVALID", "CTX_DEFAULT", "CTX_NOSTORE",
            "CTX_SERIALIZED", "CTX_WG_PRIVATE", "CTX_SHARED", "my_pe", "n_pes", "barrier_all", "sync_all", "empty",
            "zeros", "free", "put", "get", "fence", "quiet"]
+
+
+THREAD_SINGLE, THREAD_FUNNELED, THREAD_SERIALIZED, THREAD_MULTIPLE = 1, 2, 3, 4
+
+
+def init_thread(requested: int = THREAD_MULTIPLE, backend: Optional[str] = None, **kw):
+    """`init` plus the thread-level handshake of roc_shmem_init_thread (library/include/roc_shmem.hpp:160-170):
+    returns (runtime, provided).  Every backend here provides THREAD_MULTIPLE whatever is requested."""
+    rt = init(backend, **kw)
+    return rt, rt.query_thread()

@@ -429,6 +429,11 @@ struct Ctx {
   Team team;
 };
 __device__ __forceinline__ int wg_init() { return BSHMEM_THREAD_MULTIPLE; }
+// Any requested level is granted as THREAD_MULTIPLE (every device call is safe from every thread).
+__device__ __forceinline__ int wg_init_thread(int /*requested*/, int* provided) {
+  if (provided) *provided = BSHMEM_THREAD_MULTIPLE;
+  return BSHMEM_OK;
+}
 __device__ __forceinline__ void wg_finalize() {}
 __device__ __forceinline__ int query_thread() { return BSHMEM_THREAD_MULTIPLE; }
 // Called by every thread of the block; the handle is valid after the call returns.

@@ -44,6 +44,18 @@ def fp8_lib() -> C.CDLL:
         lib.bshmem_fp8_ag_error_site.argtypes = [VP, I]
         lib.bshmem_fp8_ag_destroy.restype = I
         lib.bshmem_fp8_ag_destroy.argtypes = [VP]
+        lib.bshmem_fp8_rs_staging_bytes.restype = C.c_uint64
+        lib.bshmem_fp8_rs_staging_bytes.argtypes = [I, I]
+        lib.bshmem_fp8_rs_signal_bytes.restype = C.c_uint64
+        lib.bshmem_fp8_rs_signal_bytes.argtypes = [I, I, I]
+        lib.bshmem_fp8_rs_plan.restype = I
+        lib.bshmem_fp8_rs_plan.argtypes = [VP, I, I, I, VP, VP, C.POINTER(VP)]
+        lib.bshmem_fp8_rs_run.restype = I
+        lib.bshmem_fp8_rs_run.argtypes = [VP, VP, VP, VP, VP, VP, I, VP, I, I]
+        lib.bshmem_fp8_rs_error_site.restype = I
+        lib.bshmem_fp8_rs_error_site.argtypes = [VP, I]
+        lib.bshmem_fp8_rs_destroy.restype = I
+        lib.bshmem_fp8_rs_destroy.argtypes = [VP]
         _declared = True
     return lib
 
@@ -201,21 +213,7 @@ class GemmReduceScatterFp8:
     def __init__(self, rt, M: int, N: int, K: int, timeout_ms: int = 2000, max_ctas: int = 0):
         self.rt, self.M, self.N, self.K = rt, M, N, K
         self.lib = fp8_lib()
-        lib, VP, I = self.lib, C.c_void_p, C.c_int
-        if not getattr(lib, "_rs_declared", False):
-            lib.bshmem_fp8_rs_staging_bytes.restype = C.c_uint64
-            lib.bshmem_fp8_rs_staging_bytes.argtypes = [I, I]
-            lib.bshmem_fp8_rs_signal_bytes.restype = C.c_uint64
-            lib.bshmem_fp8_rs_signal_bytes.argtypes = [I, I, I]
-            lib.bshmem_fp8_rs_plan.restype = I
-            lib.bshmem_fp8_rs_plan.argtypes = [VP, I, I, I, VP, VP, C.POINTER(VP)]
-            lib.bshmem_fp8_rs_run.restype = I
-            lib.bshmem_fp8_rs_run.argtypes = [VP, VP, VP, VP, VP, VP, I, VP, I, I]
-            lib.bshmem_fp8_rs_error_site.restype = I
-            lib.bshmem_fp8_rs_error_site.argtypes = [VP, I]
-            lib.bshmem_fp8_rs_destroy.restype = I
-            lib.bshmem_fp8_rs_destroy.argtypes = [VP]
-            lib._rs_declared = True
+        lib = self.lib
         P = rt.n_pes
         self.timeout_ms, self.max_ctas = timeout_ms, max_ctas
         self.staging = rt.empty((lib.bshmem_fp8_rs_staging_bytes(M, N),), torch.uint8, align=1024)
