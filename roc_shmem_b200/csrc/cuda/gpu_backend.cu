@@ -472,6 +472,8 @@ class GpuBackend final : public Backend {
     cudaMemset(local_base() + BSHMEM_OFF_FLAGS + (uint64_t)slot * BSHMEM_MAX_COLL_CTAS * BSHMEM_MAX_PES * 8, 0,
                (uint64_t)BSHMEM_MAX_COLL_CTAS * BSHMEM_MAX_PES * 8);
     cudaMemset(local_base() + BSHMEM_OFF_EPOCHS + (uint64_t)slot * BSHMEM_MAX_COLL_CTAS * 8, 0, BSHMEM_MAX_COLL_CTAS * 8);
+    // the slot's low-latency allreduce block: epoch word and per-sender slots start from zero for the new team
+    cudaMemset(local_base() + BSHMEM_OFF_LLT + (uint64_t)slot * BSHMEM_LLT_TEAM_BYTES, 0, BSHMEM_LLT_TEAM_BYTES);
   }
 
   int cuda_fail(const char* what, cudaError_t e) {

@@ -275,7 +275,8 @@ __device__ __forceinline__ void split_range(size_t n, int parts, int idx, size_t
 constexpr size_t kOneShotBytes = 64 * 1024;   // below this every PE reduces the whole vector itself
 
 static_assert(BSHMEM_OFF_SCRATCH + BSHMEM_SCRATCH_BYTES <= BSHMEM_OFF_LL && BSHMEM_OFF_LL + BSHMEM_LL_BYTES <= BSHMEM_OFF_SLAB &&
-              BSHMEM_OFF_SLAB + BSHMEM_SLAB_BYTES <= BSHMEM_OFF_LLB && BSHMEM_OFF_LLB + BSHMEM_LLB_BYTES <= BSHMEM_INTERNAL_BYTES,
+              BSHMEM_OFF_SLAB + BSHMEM_SLAB_BYTES <= BSHMEM_OFF_LLB && BSHMEM_OFF_LLB + BSHMEM_LLB_BYTES <= BSHMEM_OFF_LLT &&
+              BSHMEM_OFF_LLT + (uint64_t)BSHMEM_MAX_TEAMS * BSHMEM_LLT_TEAM_BYTES <= BSHMEM_INTERNAL_BYTES,
               "internal heap regions overlap");
 
 // Low-latency allreduce for small vectors on the world team, single block: ONE NVLink exchange instead of
@@ -295,8 +296,9 @@ __device__ __forceinline__ int team_reduce_ll(const State& s, const Team& t, int
   constexpr int kWords = kUnit / 4, kElems = kUnit / (int)sizeof(T);
   __shared__ unsigned long long ll_epoch;
   __shared__ int ll_status;
-  const size_t region = epoch_in ? BSHMEM_OFF_LLB : BSHMEM_OFF_LL;
-  const size_t slot_bytes = epoch_in ? BSHMEM_LLB_SLOT_BYTES : BSHMEM_LL_SLOT_BYTES;
+  // world team: host-epoch region or the small region; any other team: that team's own block
+  const size_t region = epoch_in ? BSHMEM_OFF_LLB : t.slot == 0 ? BSHMEM_OFF_LL : BSHMEM_OFF_LLT + (size_t)t.slot * BSHMEM_LLT_TEAM_BYTES;
+  const size_t slot_bytes = epoch_in ? BSHMEM_LLB_SLOT_BYTES : t.slot == 0 ? BSHMEM_LL_SLOT_BYTES : BSHMEM_LLT_SLOT_BYTES;
   char* my_base = s.heap_base[s.my_pe] + region;
   if (threadIdx.x == 0) {
     ll_epoch = epoch_in ? epoch_in : *reinterpret_cast<unsigned long long*>(my_base) + 1;
@@ -370,10 +372,14 @@ template <typename T>
 __device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
                                            int cta = 0, int ncta = 1, unsigned long long ll_epoch = 0) {
   // small vectors on the world team: one exchange (the condition is the same on every PE: symmetric addresses)
-  if (t.slot == 0 && t.size == s.n_pes && (n * sizeof(T)) % (sizeof(T) > 4 ? sizeof(T) : 4) == 0 && n > 0 &&
+  if ((n * sizeof(T)) % (sizeof(T) > 4 ? sizeof(T) : 4) == 0 && n > 0 &&
       ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & (sizeof(T) > 4 ? 7 : 3)) == 0) {
-    if (ncta == 1 && n * sizeof(T) <= BSHMEM_LL_PAYLOAD_BYTES) return team_reduce_ll<T>(s, t, op, dest, source, n);
-    if (ll_epoch != 0 && n * sizeof(T) <= BSHMEM_LLB_PAYLOAD_BYTES) return team_reduce_ll<T>(s, t, op, dest, source, n, ll_epoch, cta, ncta);
+    if (t.slot == 0 && t.size == s.n_pes) {
+      if (ncta == 1 && n * sizeof(T) <= BSHMEM_LL_PAYLOAD_BYTES) return team_reduce_ll<T>(s, t, op, dest, source, n);
+      if (ll_epoch != 0 && n * sizeof(T) <= BSHMEM_LLB_PAYLOAD_BYTES) return team_reduce_ll<T>(s, t, op, dest, source, n, ll_epoch, cta, ncta);
+    } else if (t.slot > 0 && t.slot < BSHMEM_MAX_TEAMS && ncta == 1 && n * sizeof(T) <= BSHMEM_LLT_PAYLOAD_BYTES) {
+      return team_reduce_ll<T>(s, t, op, dest, source, n);
+    }
   }
   const T* srcs[BSHMEM_MAX_PES];
   T* dsts[BSHMEM_MAX_PES];

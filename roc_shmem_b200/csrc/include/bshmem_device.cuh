@@ -33,6 +33,12 @@
 #define BSHMEM_LLB_PAYLOAD_BYTES (512ull << 10)
 #define BSHMEM_LLB_SLOT_BYTES (2 * BSHMEM_LLB_PAYLOAD_BYTES)
 #define BSHMEM_LLB_BYTES (2ull * BSHMEM_MAX_PES * BSHMEM_LLB_SLOT_BYTES)
+/* The same for every other team (single block, at most 1 KiB): 36 MiB .. 38.6 MiB, [team slot][64-byte header with the
+ * team's epoch word, then 2 parities][sender index][2 KiB]; zeroed when a team slot is (re)assigned.                 */
+#define BSHMEM_OFF_LLT (36ull << 20)
+#define BSHMEM_LLT_PAYLOAD_BYTES 1024ull
+#define BSHMEM_LLT_SLOT_BYTES (2 * BSHMEM_LLT_PAYLOAD_BYTES)
+#define BSHMEM_LLT_TEAM_BYTES (64 + 2ull * BSHMEM_MAX_PES * BSHMEM_LLT_SLOT_BYTES)
 #define BSHMEM_OFF_FLAGS 0ull                                   /* [team][cta][pe] u64, written by peers   */
 #define BSHMEM_FLAGS_BYTES ((uint64_t)BSHMEM_MAX_TEAMS * BSHMEM_MAX_COLL_CTAS * BSHMEM_MAX_PES * 8)
 #define BSHMEM_OFF_EPOCHS (BSHMEM_OFF_FLAGS + BSHMEM_FLAGS_BYTES) /* [team][cta] u64, local only           */

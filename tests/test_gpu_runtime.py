@@ -296,3 +296,28 @@ def test_group_allreduce_low_latency_path(group, dtype, n, op):
                 assert torch.allclose(d.to(wide), ref, rtol=2e-2 if dtype == torch.bfloat16 else 1e-6), (rep, dtype)
             else:
                 assert torch.equal(d.to(wide), ref), (rep, dtype)
+
+
+def test_group_team_allreduce_low_latency_path(group):
+    """Teams other than the world team have their own one-exchange slots (vectors of at most 1 KiB, one block);
+    two disjoint teams use theirs independently and repeated calls alternate the slot parity."""
+    from roc_shmem_b200 import gpu
+    even = group.team_split(0, 0, 2, 2)                   # PEs {0, 2}
+    odd = group.team_split(0, 1, 2, 2)                    # PEs {1, 3}
+    assert even[0] == even[2] > 0 and odd[1] == odd[3] > 0 and even[0] != odd[1]
+    n = 200
+    src = group.empty((n,), torch.float32)
+    dst = group.empty((n,), torch.float32)
+    dst2 = group.empty((n,), torch.float32)
+    # a slot number means "my team in that slot" on every PE, and PEs outside a team may hold an older team under the
+    # same number, so each team's result goes to its own buffer and only its members' copies are checked
+    for rep in range(6):
+        for i in range(group.n_pes):
+            src[i].copy_(torch.arange(n, device="cuda", dtype=torch.float32) + 10 * i + rep)
+            dst[i].zero_()
+            dst2[i].zero_()
+        group.collective(gpu.COLL_REDUCE, dst, src, n, dtype=torch.float32, op=0, team_slot=even[0], ctas=1)
+        group.collective(gpu.COLL_REDUCE, dst2, src, n, dtype=torch.float32, op=2, team_slot=odd[1], ctas=1)
+        base = torch.arange(n, device="cuda", dtype=torch.float32) + rep
+        assert torch.equal(dst[0], 2 * base + 20) and torch.equal(dst[2], 2 * base + 20)      # sum over PEs 0 and 2
+        assert torch.equal(dst2[1], base + 30) and torch.equal(dst2[3], base + 30)            # max over PEs 1 and 3
