@@ -196,7 +196,24 @@ struct FSmem {
   __device__ __forceinline__ volatile int* abort_flag() const {
     return reinterpret_cast<volatile int*>(gen + FSMEM_TILES + 8 * (2 * FSTAGES + 4) + 8);
   }
+  // reduce-scatter variant: how many epilogue warps have completed their store of the tile with this parity
+  __device__ __forceinline__ int* rs_count(int parity) const {
+    return reinterpret_cast<int*>(gen + FSMEM_TILES + 8 * (2 * FSTAGES + 4) + 16) + parity;
+  }
 };
+
+// Called by lane 0 of an epilogue warp once its own TMA store of a tile is complete: the last of the 16 warps to
+// arrive publishes the whole tile with ONE system-scope fence and ONE signal (no warp ever waits for another; the
+// epilogue warps stay within one k-block of each other, so two alternating counters are enough).
+__device__ __forceinline__ void rs_publish(int* count, uint64_t* sig) {
+  __threadfence();
+  if (atomicAdd(count, 1) == FEPI_WARPS - 1) {
+    *reinterpret_cast<volatile int*>(count) = 0;
+    ptx::fence_proxy_async_all();
+    ptx::fence_acq_rel_sys();
+    ptx::red_release_sys_add_u64(sig, 1);
+  }
+}
 
 template <int kMode>
 __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs* rs, uint8_t* smem_raw) {
@@ -216,6 +233,8 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
 
   if (threadIdx.x == 0) {
     *L.abort_flag() = 0;
+    *L.rs_count(0) = 0;
+    *L.rs_count(1) = 0;
     for (int s = 0; s < FSTAGES; ++s) { ptx::mbar_init(L.full(s), 1); ptx::mbar_init(L.empty(s), 1); }
     for (int b = 0; b < 2; ++b) { ptx::mbar_init(L.part_full(b), 1); ptx::mbar_init(L.part_empty(b), FEPI_WARPS); }
     ptx::fence_mbar_init();
@@ -302,6 +321,7 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
     const int quarter = warp & 3;          // TMEM lanes 32*quarter.. belong to this warp
     const int cg = ew >> 2;                // columns [64*cg, 64*cg + 64) of the tile
     uint64_t* pend_sig = nullptr;          // reduce-scatter variant: signal word of the tile whose store is in flight
+    int pend_par = 0, tiles_done = 0;      // ... and which of the two arrival counters that tile uses
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -365,9 +385,7 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
         if (lane == 0) {
           ptx::tma_wait_group<0>();
           if (pend_sig != nullptr) {
-            ptx::fence_proxy_async_all();
-            ptx::fence_acq_rel_sys();
-            ptx::red_release_sys_add_u64(pend_sig, 1);
+            rs_publish(L.rs_count(pend_par), pend_sig);
             pend_sig = nullptr;
           }
         }
@@ -397,19 +415,17 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
           const int owner = m_blk / rs->blocks_per_rank, m_in = m_blk - owner * rs->blocks_per_rank;
           ptx::tma_store_2d(&rs->map_stage[owner], L.epi(ew), n_blk * FBN + cg * 64, m_in * FBM + quarter * 32);
           ptx::tma_commit_group();
-          // the signal (one per warp and tile) is sent once the store is complete: at the next tile's output stage
+          // the tile's signal is sent once every warp's store is complete: at the next tile's output stage
           pend_sig = reinterpret_cast<uint64_t*>(rs->sig_remote[owner] + (size_t)m_in * cp.num_n_blocks + n_blk);
+          pend_par = tiles_done & 1;
         }
       }
+      ++tiles_done;
     }
     if (lane == 0) {
       ptx::tma_wait_group<0>();
       if constexpr (kRS) {
-        if (pend_sig != nullptr) {
-          ptx::fence_proxy_async_all();
-          ptx::fence_acq_rel_sys();
-          ptx::red_release_sys_add_u64(pend_sig, 1);
-        }
+        if (pend_sig != nullptr) rs_publish(L.rs_count(pend_par), pend_sig);
       }
     }
     __syncwarp();
@@ -421,7 +437,7 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
   if constexpr (kRS) {
     // ---- reduce the partials of the tiles this PE owns: owned tile t goes to CTA t % grid ----
     const int owned = rs->blocks_per_rank * cp.num_n_blocks;
-    const unsigned long long want = (unsigned long long)FEPI_WARPS * rs->P * rs->call;
+    const unsigned long long want = (unsigned long long)rs->P * rs->call;      // one signal per source PE and tile
     const size_t slot = (size_t)(cp.M / rs->P) * cp.N;           // elements per source slot
     for (int t = blockIdx.x; t < owned && !*L.abort_flag(); t += gridDim.x) {
       if (threadIdx.x == 0) wait_ge<true>(rs->sig_local + t, want, g, ERR_F8_RS_SIGNAL);
