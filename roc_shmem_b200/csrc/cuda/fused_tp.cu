@@ -22,14 +22,16 @@
 // neither GEMMs nor fused collectives); the signalling follows its put + flag idiom
 // (library/src/gpu_ib/context_ib_tmpl_device.hpp:184-236).
 #include <cstdlib>
+#include <memory>
 #include <vector>
 
 #include "../include/bshmem_device.cuh"
-#include "gemm_core.cuh"
+#include "gemm_pair.cuh"
 #include "tma_host.h"
 
 using namespace bshmem;
-using namespace bshmem::gemm;
+using namespace bshmem::gemm2;
+using gemm::wait_ge;
 
 namespace {
 
@@ -41,180 +43,139 @@ constexpr int kMaxPes = BSHMEM_MAX_PES;
 struct RsParams {
   CoreParams core;
   CUtensorMap map_a, map_b;
-  CUtensorMap map_out[kMaxPes];                 // owner q's staging slot of this rank: [rows_per_owner, N]
+  CUtensorMap map_stage[kMaxPes];               // owner q's staging slot of this rank: [rows_per_owner, N]
+  CUtensorMap map_out;                          // this rank's reduced rows: [rows_per_owner, N] (ldo)
   int P, my_rank, blocks_per_owner, rows_per_owner;
-  unsigned long long* sig_remote[kMaxPes];      // owner q's signal words, one per (row-block, n-block)
+  unsigned long long* sig_remote[kMaxPes];      // owner q's signal words, one per (row-block, n-block, 128-row half)
   const unsigned long long* sig_local;
-  unsigned long long expect;                    // value of a tile's signal once all P partials of this call landed
+  unsigned long long expect;                    // value of a signal once the P-1 peers' partials of this call landed
   const __nv_bfloat16* staging_local;           // [P][rows_per_owner][N] (this call's parity)
-  __nv_bfloat16* out;                           // [rows_per_owner, N]
-  long long ldo;
-  unsigned int* ticket;                         // local [2]: reduction work counter of this call's parity
-  unsigned long long call;
-  int tune;                                     // bit 0: no reduction during the GEMM, bit 1: skip the reduction (timing experiments only)
 };
 
 struct GemmRs : PolicyDefaults {
   using Params = RsParams;
-  static constexpr int kElemBytes = 2;
-  static constexpr uint32_t kIdesc = ptx::umma_idesc(1, 1, UMMA_M, UMMA_N);
-  static constexpr bool kWaitStoresPerTile = true;   // the signal must follow the completed stores
+  // deferred publication of the previous tile this warp sent to a peer
+  struct EpiState { int pending, owner, idx, ord; };
   __device__ static __forceinline__ const CoreParams& core(const Params& p) { return p.core; }
   __device__ static __forceinline__ const CUtensorMap* map_a(const Params& p) { return &p.map_a; }
   __device__ static __forceinline__ const CUtensorMap* map_b(const Params& p) { return &p.map_b; }
-  // Sub-round major: in sub-round s every rank visits the owners (me+1, me+2, ..., me) and computes
-  // row-block s of each, so the P ranks always target P different owners and all partials of an
-  // owner's row-block s have been sent when sub-round s ends.
+  // First every tile whose rows another PE owns: in sub-round s every rank visits the owners me+1, me+2, ...,
+  // me-1 and computes row-block s of each, so the P ranks always send to P different owners.  Then the tiles of
+  // this PE's own rows, whose epilogue adds the P-1 partials that arrived meanwhile and writes the result.
   __device__ static __forceinline__ void tile_coords(const Params& p, int tile, int* m_blk, int* n_blk) {
-    int per_sub = p.P * p.core.num_n_blocks;
-    int sub = tile / per_sub, rem = tile - sub * per_sub;
-    int step = rem / p.core.num_n_blocks;
-    *n_blk = rem - step * p.core.num_n_blocks;
-    int owner = (p.my_rank + 1 + step) % p.P;
-    *m_blk = owner * p.blocks_per_owner + sub;
-  }
-  __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * BM; }
-  __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    ptx::umma_f16(d, a, b, idesc, acc);
-  }
-  __device__ static __forceinline__ uint32_t pack(uint32_t lo, uint32_t hi, const Params&, int, int) {
-    return pack_bf16(__uint_as_float(lo), __uint_as_float(hi));
+    const int num_n = p.core.num_n_blocks;
+    const int send_tiles = (p.P - 1) * p.blocks_per_owner * num_n;
+    if (tile < send_tiles) {
+      int per_sub = (p.P - 1) * num_n;
+      int sub = tile / per_sub, rem = tile - sub * per_sub;
+      int step = rem / num_n;
+      *n_blk = rem - step * num_n;
+      int owner = (p.my_rank + 1 + step) % p.P;
+      *m_blk = owner * p.blocks_per_owner + sub;
+    } else {
+      int t = tile - send_tiles;
+      int sub = t / num_n;
+      *n_blk = t - sub * num_n;
+      *m_blk = p.my_rank * p.blocks_per_owner + sub;
+    }
   }
   __device__ static __forceinline__ void out_target(const Params& p, int row, int col, const CUtensorMap** map, int* x, int* y) {
     int owner = row / p.rows_per_owner;
-    *map = &p.map_out[owner];
+    *map = owner == p.my_rank ? &p.map_out : &p.map_stage[owner];
     *x = col;
     *y = row - owner * p.rows_per_owner;
   }
-  // The warp's TMA stores of this tile are complete: publish them and count one arrival on the owner.
-  __device__ static __forceinline__ void tile_done(const Params& p, int m_blk, int n_blk, int, int lane) {
+  // The warp's TMA stores of the tile it sent last are complete: count it on the CTA's counter of that tile; the
+  // last of the CTA's eight warps publishes the CTA's half of the tile with ONE system-scope fence and ONE signal.
+  // Counters are monotonic and keyed by the tile ordinal (mod 4); warps of a CTA are never more than two tiles
+  // apart (two accumulators), so a counter is only shared by tiles whose counts cannot overlap in time.
+  __device__ static __forceinline__ void flush(const Params& p, const Smem& L, EpiState& st, int lane) {
+    if (!st.pending) return;
+    st.pending = 0;
     if (lane == 0) {
-      int owner = m_blk / p.blocks_per_owner;
-      int idx = (m_blk - owner * p.blocks_per_owner) * p.core.num_n_blocks + n_blk;
+      ptx::tma_wait_group<0>();
       ptx::fence_proxy_async_all();
-      ptx::fence_acq_rel_sys();
-      ptx::red_release_sys_add_u64(reinterpret_cast<uint64_t*>(p.sig_remote[owner] + idx), 1);
+      __threadfence();
+      unsigned int old = atomicAdd(&L.scratch()[st.ord & 3], 1u);
+      if (((old + 1) & (NUM_EPI_WARPS - 1)) == 0) {
+        ptx::fence_acq_rel_sys();
+        ptx::red_release_sys_add_u64(reinterpret_cast<uint64_t*>(p.sig_remote[st.owner] + st.idx), 1);
+      }
     }
   }
-  // ---- reduction of the partials this PE owns --------------------------------------------------
-  // Work unit: 8 rows x 256 columns of one owned tile (32 units per tile), handed out by a ticket
-  // counter in tile order, which is also the order in which the tiles' partials arrive.
-  static constexpr int kUnitsPerTile = BM / 8;
-  // PP = number of partials (compile time), R = rows whose loads are issued together (PP * R loads in flight)
-  template <int PP, int R>
-  __device__ static __forceinline__ void reduce_rows(const Params& p, int r0, long long c) {
+  __device__ static __forceinline__ bool tile_begin(const Params& p, const Smem& L, EpiState& st, const Chunk& ck, int, int lane, Guard& g) {
+    flush(p, L, st, lane);
+    const int owner = ck.m_blk / p.blocks_per_owner;
+    if (owner != p.my_rank || p.P == 1) return true;
+    // own tile: the P-1 partials of this CTA's 128 rows must have landed in the local staging
+    const int idx = ((ck.m_blk - owner * p.blocks_per_owner) * p.core.num_n_blocks + ck.n_blk) * 2 + ck.half;
+    int ok = 1;
+    if (lane == 0) ok = wait_ge<true>(p.sig_local + idx, p.expect, g, ERR_PEER_SIGNAL) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  }
+  // Own tile: add the peers' bf16 partials of this 32x64 chunk to the fp32 accumulators, in source order
+  // (fixed, so results are reproducible run to run).  A partial chunk is fetched with fully coalesced 16-byte
+  // loads (lane -> row lane/8 + 4i, piece lane%8), parked in the warp's swizzled staging buffer and read back
+  // row-per-lane; the next partial's loads are in flight meanwhile.
+  __device__ static __forceinline__ void adjust(const Params& p, const Smem& L, EpiState&, const Chunk& ck, float (&f)[64], int ew, int lane) {
+    const int owner = ck.m_blk / p.blocks_per_owner;
+    if (owner != p.my_rank || p.P == 1) return;
     const long long N = p.core.N;
-#pragma unroll 1
-    for (int j = 0; j < 8; j += R) {
-      uint4 x[R][PP];
+    const int r_local = ck.row0 - owner * p.rows_per_owner;
+    const int pr = lane >> 3, pc = lane & 7;
+    const uint32_t buf = L.epi(ew);
+    const __nv_bfloat16* src0 = p.staging_local + (long long)(r_local + pr) * N + ck.col0 + pc * 8;
+    const long long slot = (long long)p.rows_per_owner * N;
+    uint4 x[8];
+    int s = p.my_rank == 0 ? 1 : 0;
 #pragma unroll
-      for (int q = 0; q < R; ++q)
+    for (int i = 0; i < 8; ++i) x[i] = ptx::ld_relaxed_v4(src0 + s * slot + (long long)(4 * i) * N);
+    while (true) {
 #pragma unroll
-        for (int s = 0; s < PP; ++s)
-          x[q][s] = ptx::ld_relaxed_v4(p.staging_local + ((long long)s * p.rows_per_owner + r0 + j + q) * N + c);
-#pragma unroll
-      for (int q = 0; q < R; ++q) {
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-#pragma unroll
-        for (int s = 0; s < PP; ++s) {
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x[q][s]);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float2 f = __bfloat1622float2(h[e]);
-            acc[2 * e] += f.x;
-            acc[2 * e + 1] += f.y;
-          }
-        }
-        uint4 o;
-        o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
-        o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(p.out + (long long)(r0 + j + q) * p.ldo + c) = o;
+      for (int i = 0; i < 8; ++i) {
+        const int row = pr + 4 * i;
+        const uint32_t dst = buf + row * 128 + ((pc ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(x[i].x), "r"(x[i].y), "r"(x[i].z), "r"(x[i].w) : "memory");
       }
-    }
-  }
-  __device__ static __forceinline__ void reduce_unit(const Params& p, int tile_i, int part, int lane) {
-    const int num_n = p.core.num_n_blocks;
-    const int blk = tile_i / num_n, n_blk = tile_i - blk * num_n;
-    const int r0 = blk * BM + part * 8;
-    const long long c = (long long)n_blk * BN + lane * 8;      // one 16-byte vector per lane and row
-    switch (p.P) {
-      case 1: reduce_rows<1, 8>(p, r0, c); break;
-      case 2: reduce_rows<2, 8>(p, r0, c); break;
-      case 4: reduce_rows<4, 4>(p, r0, c); break;
-      case 8: reduce_rows<8, 2>(p, r0, c); break;
-      default: {
-        const long long N = p.core.N;
-        for (int j = 0; j < 8; ++j) {
-          float acc[8];
+      __syncwarp();
+      int next = s + 1;
+      if (next == p.my_rank) ++next;
+      if (next < p.P) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-          for (int s = 0; s < p.P; ++s) {
-            uint4 x = ptx::ld_relaxed_v4(p.staging_local + ((long long)s * p.rows_per_owner + r0 + j) * N + c);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+        for (int i = 0; i < 8; ++i) x[i] = ptx::ld_relaxed_v4(src0 + next * slot + (long long)(4 * i) * N);
+      }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
-          }
-          uint4 o;
-          o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
-          o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
-          *reinterpret_cast<uint4*>(p.out + (long long)(r0 + j) * p.ldo + c) = o;
+      for (int j = 0; j < 8; ++j) {
+        uint4 y;
+        const uint32_t a = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(y.x), "=r"(y.y), "=r"(y.z), "=r"(y.w) : "r"(a) : "memory");
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 v = __bfloat1622float2(h[e]);
+          f[j * 8 + 2 * e] += v.x;
+          f[j * 8 + 2 * e + 1] += v.y;
         }
       }
+      __syncwarp();
+      if (next >= p.P) break;
+      s = next;
     }
   }
-  // Units are dealt out statically: epilogue warp w of CTA c owns units c*8+w, c*8+w + G*8, ... (G = grid
-  // size), in tile order, which is also the order in which the partials arrive.  Its cursor (how many of
-  // its units are done) lives in the warp's state word, so no atomics and no contention are involved.
-  __device__ static __forceinline__ int unit_of(const Params& p, int ew, int k) {
-    return k * (int)gridDim.x * NUM_EPI_WARPS + (int)blockIdx.x * NUM_EPI_WARPS + ew;
+  __device__ static __forceinline__ void tile_end(const Params& p, const Smem&, EpiState& st, const Chunk& ck, int, int) {
+    const int owner = ck.m_blk / p.blocks_per_owner;
+    if (owner == p.my_rank) return;
+    st.pending = 1;
+    st.owner = owner;
+    st.idx = ((ck.m_blk - owner * p.blocks_per_owner) * p.core.num_n_blocks + ck.n_blk) * 2 + ck.half;
+    st.ord = ck.ordinal;
   }
-  // During the GEMM: reduce my next unit only if its partials are already complete.  This must never
-  // block — the warp still owes its CTA an epilogue, and two CTAs whose epilogue warps wait for each
-  // other's current tile would deadlock.
-  __device__ static __forceinline__ bool idle_work(const Params& p, int ew, int lane, Guard&, int, volatile int* cursor) {
-    if (p.tune & 1) return false;
-    const int total = p.blocks_per_owner * p.core.num_n_blocks * kUnitsPerTile;
-    const int k = *cursor;
-    const int u = unit_of(p, ew, k);
-    if (u >= total) return false;
-    const int tile_i = u / kUnitsPerTile;
-    int ready = 0;
-    if (lane == 0) ready = ptx::ld_acquire_sys_u64(reinterpret_cast<const uint64_t*>(p.sig_local + tile_i)) >= p.expect;
-    ready = __shfl_sync(0xffffffffu, ready, 0);
-    if (!ready) return false;
-    reduce_unit(p, tile_i, u - tile_i * kUnitsPerTile, lane);
-    __syncwarp();
-    if (lane == 0) *cursor = k + 1;
-    __syncwarp();
-    return true;
-  }
-  // After the CTA's last tile its epilogue warps finish their remaining units, waiting (bounded) for the
-  // partials; nobody can be waiting for this CTA any more.
-  __device__ static __forceinline__ void tail(const Params& p, const Smem& L, Guard& g) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp < 2 || (p.tune & 2)) return;
-    const int ew = warp - 2;
-    const int total = p.blocks_per_owner * p.core.num_n_blocks * kUnitsPerTile;
-    int waited_tile = -1;
-    for (int k = *L.warp_state(warp);; ++k) {
-      const int u = unit_of(p, ew, k);
-      if (u >= total) break;
-      const int tile_i = u / kUnitsPerTile;
-      if (tile_i != waited_tile) {
-        int ok = 1;
-        if (lane == 0) ok = wait_ge<true>(p.sig_local + tile_i, p.expect, g, ERR_PEER_SIGNAL) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        waited_tile = tile_i;
-      }
-      reduce_unit(p, tile_i, u - tile_i * kUnitsPerTile, lane);
-    }
+  __device__ static __forceinline__ void epilogue_drain(const Params& p, const Smem& L, EpiState& st, int, int lane, Guard&) {
+    flush(p, L, st, lane);
   }
 };
 
-__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_rs_kernel(const __grid_constant__ RsParams prm) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1) gemm_rs_kernel(const __grid_constant__ RsParams prm) {
   extern __shared__ uint8_t smem_raw[];
   gemm_mainloop<GemmRs>(prm, smem_raw);
 }
@@ -244,8 +205,6 @@ struct AgParams {
 
 struct AgGemm : PolicyDefaults {
   using Params = AgParams;
-  static constexpr int kElemBytes = 2;
-  static constexpr uint32_t kIdesc = ptx::umma_idesc(1, 1, UMMA_M, UMMA_N);
   __device__ static __forceinline__ const CoreParams& core(const Params& p) { return p.core; }
   __device__ static __forceinline__ const CUtensorMap* map_a(const Params& p) { return &p.map_a; }
   __device__ static __forceinline__ const CUtensorMap* map_b(const Params& p) { return &p.map_b; }
@@ -256,13 +215,6 @@ struct AgGemm : PolicyDefaults {
     int src = (p.my_rank + step) % p.P;
     *m_blk = src * p.blocks_per_rank + rem % p.blocks_per_rank;
     *n_blk = rem / p.blocks_per_rank;
-  }
-  __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * BM; }
-  __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    ptx::umma_f16(d, a, b, idesc, acc);
-  }
-  __device__ static __forceinline__ uint32_t pack(uint32_t lo, uint32_t hi, const Params&, int, int) {
-    return pack_bf16(__uint_as_float(lo), __uint_as_float(hi));
   }
   __device__ static __forceinline__ void out_target(const Params& p, int row, int col, const CUtensorMap** map, int* x, int* y) {
     *map = (row < p.core.M && col < p.core.N) ? &p.map_c : nullptr;
@@ -326,7 +278,7 @@ struct AgGemm : PolicyDefaults {
     }
     return true;
   }
-  __device__ static __forceinline__ void epilogue_drain(const Params& p, int ew, int lane, Guard& g) {
+  __device__ static __forceinline__ void epilogue_drain(const Params& p, const Smem&, EpiState&, int ew, int lane, Guard& g) {
     while (idle_work(p, ew, lane, g, 0)) {}
   }
   // Before the kernel ends, CTA 0 makes sure every peer has finished pulling this rank's rows.
@@ -336,7 +288,7 @@ struct AgGemm : PolicyDefaults {
   }
 };
 
-__global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_constant__ AgParams prm) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_constant__ AgParams prm) {
   extern __shared__ uint8_t smem_raw[];
   gemm_mainloop<AgGemm>(prm, smem_raw);
 }
@@ -345,10 +297,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_co
 // host side
 // =====================================================================================
 struct Plan {
-  int kind;                 // 0 = gemm->rs, 1 = ag->gemm
-  int device, sms;
+  int kind = 0;             // 0 = gemm->rs, 1 = ag->gemm
+  int device = 0, pairs = 0;
   bshmem_dev_state_t st;
-  int M, N, K;
+  int M = 0, N = 0, K = 0;
   unsigned long long call = 0;
   int* err = nullptr;
   // rs
@@ -360,6 +312,12 @@ struct Plan {
   unsigned long long* arrived = nullptr;
   unsigned long long* src_pulled = nullptr;
   unsigned int* ticket = nullptr;
+  ~Plan() {
+    if (err) cudaFree(err);
+    if (arrived) cudaFree(arrived);
+    if (src_pulled) cudaFree(src_pulled);
+    if (ticket) cudaFree(ticket);
+  }
 };
 
 template <typename T> T* peer_ptr(const bshmem_dev_state_t& st, T* local, int pe) {
@@ -367,12 +325,14 @@ template <typename T> T* peer_ptr(const bshmem_dev_state_t& st, T* local, int pe
 }
 
 int common_init(Plan* p) {
+  int sms = 0;
   BSHMEM_CUDA_TRY(cudaGetDevice(&p->device));
-  BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&p->sms, cudaDevAttrMultiProcessorCount, p->device));
+  BSHMEM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device));
   BSHMEM_CUDA_TRY(cudaMalloc(&p->err, sizeof(int)));
   BSHMEM_CUDA_TRY(cudaMemset(p->err, 0, sizeof(int)));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+  p->pairs = p->kind == 0 ? max_resident_pairs(gemm_rs_kernel, sms) : max_resident_pairs(ag_gemm_kernel, sms);
   return 0;
 }
 
@@ -382,20 +342,28 @@ bool in_heap(const bshmem_dev_state_t& st, const void* p, uint64_t n) {
   return c >= b && (uint64_t)(c - b) + n <= st.heap_bytes;
 }
 
+int grid_ctas(const Plan* p, int tiles, int max_ctas) {
+  int pairs = p->pairs;
+  if (max_ctas > 1 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
+  if (tiles < pairs) pairs = tiles;
+  return 2 * pairs;
+}
+
 }  // namespace
 
 extern "C" {
 
 const char* bshmem_fused_last_error() { return host::last_error().c_str(); }
 
-// Bytes of symmetric memory the GEMM->RS plan needs: staging (2 parities x P slots x M/P x N bf16) and signals.
+// Bytes of symmetric memory the GEMM->RS plan needs: staging (2 parities x P slots x M/P x N bf16) and one signal
+// word per owned tile half.
 uint64_t bshmem_fused_rs_staging_bytes(int M, int N) { return 2ull * (uint64_t)M * N * 2; }
-uint64_t bshmem_fused_rs_signal_bytes(int M, int N, int P) { return (uint64_t)(M / P / BM) * (N / BN) * 8; }
+uint64_t bshmem_fused_rs_signal_bytes(int M, int N, int P) { return (uint64_t)(M / P / BM) * (N / BN) * 2 * 8; }
 
 int bshmem_fused_rs_plan(const bshmem_dev_state_t* st, int M, int N, int K, void* staging_local, void* sig_local, void** out) {
   if (!st || !out) return 1;
   int P = st->n_pes;
-  if (M % (P * BM) || N % BN || K % 8) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % (P * BM) || N % BN || K % 8) {
     host::last_error() = "gemm_rs: needs M % (P*256) == 0, N % 256 == 0, K % 8 == 0";
     return 1;
   }
@@ -404,15 +372,13 @@ int bshmem_fused_rs_plan(const bshmem_dev_state_t* st, int M, int N, int K, void
     host::last_error() = "gemm_rs: staging / signal buffers must be symmetric allocations of the stated sizes";
     return 4;
   }
-  Plan* p = new Plan();
+  std::unique_ptr<Plan> p(new Plan());
   p->kind = 0; p->st = *st; p->M = M; p->N = N; p->K = K;
   p->staging_local = static_cast<char*>(staging_local);
   p->sig_local = static_cast<unsigned long long*>(sig_local);
-  int rc = common_init(p);
-  if (rc) { delete p; return rc; }
-  BSHMEM_CUDA_TRY(cudaMalloc(&p->ticket, sizeof(unsigned int) * 2));
-  BSHMEM_CUDA_TRY(cudaMemset(p->ticket, 0, sizeof(unsigned int) * 2));
-  *out = p;
+  int rc = common_init(p.get());
+  if (rc) return rc;
+  *out = p.release();
   return 0;
 }
 
@@ -423,7 +389,6 @@ int bshmem_fused_rs_run(void* plan, const void* x, int ldx, const void* w, int l
   if (!p || p->kind != 0) return 1;
   const int P = p->st.n_pes, me = p->st.my_pe;
   const int rows = p->M / P;
-  p->call += 1;
   RsParams prm;
   memset(&prm, 0, sizeof(prm));
   prm.core.M = p->M; prm.core.N = p->N; prm.core.K = p->K;
@@ -432,34 +397,31 @@ int bshmem_fused_rs_run(void* plan, const void* x, int ldx, const void* w, int l
   prm.core.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
   prm.core.err = p->err;
   prm.P = P; prm.my_rank = me; prm.blocks_per_owner = rows / BM; prm.rows_per_owner = rows;
-  int rc = host::make_tmap_2d(&prm.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, p->M, p->K, ldx, BM, 64);
+  int rc = host::make_tmap_2d(&prm.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, p->M, p->K, ldx, CTA_M, 64);
   if (rc) return rc;
-  rc = host::make_tmap_2d(&prm.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, p->N, p->K, ldw, BN, 64);
+  rc = host::make_tmap_2d(&prm.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, p->N, p->K, ldw, CTA_NLOAD, 64);
   if (rc) return rc;
+  rc = host::make_tmap_2d(&prm.map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, rows, p->N, ldo, 32, EPI_COLS);
+  if (rc) return rc;
+  const unsigned long long call = p->call + 1;
   const uint64_t parity_bytes = (uint64_t)p->M * p->N * 2;          // P slots x rows x N
   const uint64_t slot_bytes = (uint64_t)rows * p->N * 2;
-  char* stage_par = p->staging_local + (p->call & 1) * parity_bytes;
+  char* stage_par = p->staging_local + (call & 1) * parity_bytes;
   for (int q = 0; q < P; ++q) {
     // my slot (index me) inside owner q's staging of this parity
     char* dst = peer_ptr(p->st, stage_par, q) + (uint64_t)me * slot_bytes;
-    rc = host::make_tmap_2d(&prm.map_out[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dst, rows, p->N, p->N, 32, EPI_COLS);
+    rc = host::make_tmap_2d(&prm.map_stage[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dst, rows, p->N, p->N, 32, EPI_COLS);
     if (rc) return rc;
     prm.sig_remote[q] = peer_ptr(p->st, p->sig_local, q);
   }
   prm.sig_local = p->sig_local;
-  prm.expect = (unsigned long long)NUM_EPI_WARPS * P * p->call;
+  prm.expect = (unsigned long long)(P - 1) * call;
   prm.staging_local = reinterpret_cast<const __nv_bfloat16*>(stage_par);
-  prm.out = static_cast<__nv_bfloat16*>(out);
-  prm.ldo = ldo;
-  prm.ticket = p->ticket;
-  prm.call = p->call;
-  { const char* t = getenv("B200SHMEM_RS_TUNE"); prm.tune = t ? atoi(t) : 0; }
-  int tiles = prm.core.num_m_blocks * prm.core.num_n_blocks;
-  int ctas = p->sms;
-  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  if (tiles < ctas) ctas = tiles;
+  const int tiles = prm.core.num_m_blocks * prm.core.num_n_blocks;
+  const int ctas = grid_ctas(p, tiles, max_ctas);
   gemm_rs_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(prm);
   BSHMEM_CUDA_TRY(cudaGetLastError());
+  p->call = call;      // counted only once the kernel that sends this call's signals is enqueued
   return 0;
 }
 
@@ -469,7 +431,7 @@ uint64_t bshmem_fused_ag_flag_bytes(int P) { return 2ull * P * 8; }
 int bshmem_fused_ag_plan(const bshmem_dev_state_t* st, int M, int N, int K, void* xg_local, void* flags_local, void** out) {
   if (!st || !out) return 1;
   int P = st->n_pes;
-  if (M % (P * BM) || K % 8 || N % 8) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % (P * BM) || K % 8 || N % 8) {
     host::last_error() = "ag_gemm: needs M % (P*256) == 0, K % 8 == 0, N % 8 == 0";
     return 1;
   }
@@ -477,12 +439,12 @@ int bshmem_fused_ag_plan(const bshmem_dev_state_t* st, int M, int N, int K, void
     host::last_error() = "ag_gemm: the gathered buffer and the flags must be symmetric allocations";
     return 4;
   }
-  Plan* p = new Plan();
+  std::unique_ptr<Plan> p(new Plan());
   p->kind = 1; p->st = *st; p->M = M; p->N = N; p->K = K;
   p->xg_local = static_cast<char*>(xg_local);
   p->flags_local = static_cast<unsigned long long*>(flags_local);
-  int rc = common_init(p);
-  if (rc) { delete p; return rc; }
+  int rc = common_init(p.get());
+  if (rc) return rc;
   int nblk = M / BM;
   BSHMEM_CUDA_TRY(cudaMalloc(&p->arrived, sizeof(unsigned long long) * nblk));
   BSHMEM_CUDA_TRY(cudaMemset(p->arrived, 0, sizeof(unsigned long long) * nblk));
@@ -490,7 +452,7 @@ int bshmem_fused_ag_plan(const bshmem_dev_state_t* st, int M, int N, int K, void
   BSHMEM_CUDA_TRY(cudaMemset(p->src_pulled, 0, sizeof(unsigned long long) * kMaxPes));
   BSHMEM_CUDA_TRY(cudaMalloc(&p->ticket, sizeof(unsigned int) * 2));
   BSHMEM_CUDA_TRY(cudaMemset(p->ticket, 0, sizeof(unsigned int) * 2));
-  *out = p;
+  *out = p.release();
   return 0;
 }
 
@@ -499,7 +461,7 @@ int bshmem_fused_ag_run(void* plan, const void* w, int ldw, void* out, int ldo, 
   Plan* p = static_cast<Plan*>(plan);
   if (!p || p->kind != 1) return 1;
   const int P = p->st.n_pes, me = p->st.my_pe;
-  p->call += 1;
+  const unsigned long long call = p->call + 1;
   AgParams prm;
   memset(&prm, 0, sizeof(prm));
   prm.core.M = p->M; prm.core.N = p->N; prm.core.K = p->K;
@@ -513,9 +475,9 @@ int bshmem_fused_ag_run(void* plan, const void* w, int ldw, void* out, int ldo, 
   prm.pieces_per_block = BM * prm.pieces_per_row;
   prm.pieces_per_src = prm.blocks_per_rank * prm.pieces_per_block;
   prm.total_pieces = (P - 1) * prm.pieces_per_src;
-  int rc = host::make_tmap_2d(&prm.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p->xg_local, p->M, p->K, p->K, BM, 64);
+  int rc = host::make_tmap_2d(&prm.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p->xg_local, p->M, p->K, p->K, CTA_M, 64);
   if (rc) return rc;
-  rc = host::make_tmap_2d(&prm.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, p->N, p->K, ldw, BN, 64);
+  rc = host::make_tmap_2d(&prm.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, p->N, p->K, ldw, CTA_NLOAD, 64);
   if (rc) return rc;
   rc = host::make_tmap_2d(&prm.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, p->M, p->N, ldo, 32, EPI_COLS);
   if (rc) return rc;
@@ -530,13 +492,12 @@ int bshmem_fused_ag_run(void* plan, const void* w, int ldw, void* out, int ldo, 
   prm.ticket = p->ticket;
   prm.ready_local = p->flags_local;
   prm.done_local = p->flags_local + P;
-  prm.call = p->call;
-  int tiles = prm.core.num_m_blocks * prm.core.num_n_blocks;
-  int ctas = p->sms;
-  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  if (tiles < ctas) ctas = tiles;
+  prm.call = call;
+  const int tiles = prm.core.num_m_blocks * prm.core.num_n_blocks;
+  const int ctas = grid_ctas(p, tiles, max_ctas);
   ag_gemm_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(prm);
   BSHMEM_CUDA_TRY(cudaGetLastError());
+  p->call = call;
   return 0;
 }
 
@@ -550,13 +511,7 @@ int bshmem_fused_error_site(void* plan, int clear) {
 }
 
 int bshmem_fused_destroy(void* plan) {
-  Plan* p = static_cast<Plan*>(plan);
-  if (!p) return 0;
-  cudaFree(p->err);
-  if (p->arrived) cudaFree(p->arrived);
-  if (p->src_pulled) cudaFree(p->src_pulled);
-  if (p->ticket) cudaFree(p->ticket);
-  delete p;
+  delete static_cast<Plan*>(plan);
   return 0;
 }
 

@@ -53,8 +53,9 @@ def _check(lib, st: int, what: str) -> None:
 class GemmReduceScatter:
     """out[M/P, N] (this PE's rows) = sum over PEs r of x_r[M, K] @ w_r[N, K].T"""
 
-    algorithm = ("one kernel: tcgen05 GEMM (256x256 tiles) whose epilogue TMA-stores bf16 partial tiles into the "
-                 "owner PE's staging over NVLink + per-tile signal; CTAs then reduce the P partials of their own rows")
+    algorithm = ("one kernel: tcgen05 GEMM on CTA pairs (cta_group::2, 256x256 tiles, two TMEM accumulator stages) whose "
+                 "epilogue TMA-stores bf16 partial tiles into the owner PE's staging over NVLink + one signal per CTA and "
+                 "tile; a PE's own tiles come last and their epilogue adds the P-1 arrived partials to the fp32 accumulators")
 
     def __init__(self, rt, M: int, N: int, K: int, timeout_ms: int = 2000, max_ctas: int = 0):
         self.rt, self.M, self.N, self.K = rt, M, N, K
