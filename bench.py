@@ -130,7 +130,8 @@ def main() -> int:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)       # the baseline arm's collectives (and the bootstrap store)
-    rt = shmem.init("device", device=local_rank, heap_bytes=3 << 30)
+    # the fused kernels use plain peer stores and loads; no multicast object is bound for this job
+    rt = shmem.init("device", device=local_rank, heap_bytes=3 << 30, nvls="off")
     steps, warmup = args.steps, args.warmup
 
     def barrier():

@@ -125,10 +125,12 @@ def quiet() -> None: current().quiet()
 __all__ = ["init", "finalize", "global_exit", "current", "set_current", "Config", "Runtime", "Team", "Context",
            "ShmemError", "ShmemTimeout", "ShmemAborted", "TEAM_WORLD", "TEAM_INVALID", "CTX_DEFAULT", "CTX_NOSTORE",
            "CTX_SERIALIZED", "CTX_WG_PRIVATE", "CTX_SHARED", "my_pe", "n_pes", "barrier_all", "sync_all", "empty",
-           "zeros", "free", "put", "get", "fence", "quiet"]
+           "zeros", "free", "put", "get", "fence", "quiet", "init_thread", "THREAD_SINGLE", "THREAD_FUNNELED",
+           "THREAD_WG_FUNNELED", "THREAD_SERIALIZED", "THREAD_MULTIPLE"]
 
 
-THREAD_SINGLE, THREAD_FUNNELED, THREAD_SERIALIZED, THREAD_MULTIPLE = 1, 2, 3, 4
+# thread levels, values of bshmem_thread_level_t (csrc/include/bshmem_types.h)
+THREAD_SINGLE, THREAD_FUNNELED, THREAD_WG_FUNNELED, THREAD_SERIALIZED, THREAD_MULTIPLE = 0, 1, 2, 3, 4
 
 
 def init_thread(requested: int = THREAD_MULTIPLE, backend: Optional[str] = None, **kw):

@@ -88,6 +88,7 @@ def main() -> None:
     dev = rt.device
     rt.set_blocking(False)          # stream-ordered: calls enqueue kernels like NCCL does
     rows = []
+    failed = []                      # every failed check of this rank: {"pe", "op", "bytes"}
     ok_all = True
     torch.manual_seed(me)
 
@@ -125,6 +126,7 @@ def main() -> None:
                 good = torch.allclose(dst.float(), ref.float(), rtol=2e-2 if es == 2 else 1e-5, atol=0.3 if es == 2 else 1e-4)
                 if not good:
                     print(f"[pe {me}] allreduce_{op} {dtype} {n * es} B: max diff {(dst.float() - ref.float()).abs().max().item()}", flush=True)
+                    failed.append({"pe": me, "op": f"allreduce_{op}", "dtype": str(dtype), "bytes": n * es})
                 ok_all &= bool(good)
                 ref.copy_(src)
                 us = timed(lambda: rt.reduce(dst, src, op), iters, rt)
@@ -144,6 +146,7 @@ def main() -> None:
             good = torch.allclose(rs_dst.float(), rs_ref.float(), rtol=2e-2 if es == 2 else 1e-5, atol=0.3 if es == 2 else 1e-4)
             if not good:
                 print(f"[pe {me}] reduce_scatter {dtype} {n * es} B: max diff {(rs_dst.float() - rs_ref.float()).abs().max().item()}", flush=True)
+                failed.append({"pe": me, "op": "reduce_scatter", "dtype": str(dtype), "bytes": n * es})
             ok_all &= bool(good)
             us = timed(lambda: rt.reduce_scatter(rs_dst, src, "sum"), iters, rt)
             us_n = timed(lambda: dist.reduce_scatter_tensor(rs_ref, src), iters, rt)
@@ -164,6 +167,10 @@ def main() -> None:
         dist.all_gather_into_tensor(ref, src)
         torch.cuda.synchronize()
         good = torch.equal(dst, ref)
+        if not good:
+            bad = (dst != ref).nonzero()
+            print(f"[pe {me}] fcollect {blk * P} B: {bad.shape[0]} bytes differ, first at {int(bad[0])} (block {int(bad[0]) // blk})", flush=True)
+            failed.append({"pe": me, "op": "fcollect", "bytes": blk * P})
         ok_all &= bool(good)
         us = timed(lambda: rt.fcollect(dst, src), iters, rt)
         us_n = timed(lambda: dist.all_gather_into_tensor(ref, src), iters, rt)
@@ -175,6 +182,10 @@ def main() -> None:
         dist.all_to_all_single(ref, a_src)
         torch.cuda.synchronize()
         good = torch.equal(dst, ref)
+        if not good:
+            bad = (dst != ref).nonzero()
+            print(f"[pe {me}] alltoall {blk * P} B: {bad.shape[0]} bytes differ, first at {int(bad[0])} (block {int(bad[0]) // blk})", flush=True)
+            failed.append({"pe": me, "op": "alltoall", "bytes": blk * P})
         ok_all &= bool(good)
         us = timed(lambda: rt.alltoall(dst, a_src), iters, rt)
         us_n = timed(lambda: dist.all_to_all_single(ref, a_src), iters, rt)
@@ -250,8 +261,9 @@ def main() -> None:
     rt.set_blocking(True)
     okt = torch.tensor([int(ok_all)], device=dev)
     dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    all_failed = [f for fl in rt.bootstrap.allgather(failed, tag="coll-bench-failed") for f in fl] if P > 1 else failed
     if me == 0:
-        out = {"n_pes": P, "all_ok": bool(okt.item()), "rows": rows}
+        out = {"n_pes": P, "all_ok": bool(okt.item()), "failed_checks": all_failed, "rows": rows}
         for r in rows:
             print(json.dumps(r))
         if args.out:

@@ -35,10 +35,10 @@ class Config:
     debug: bool = False                # bounds checks, verbose native errors
     profile: bool = True               # API-call counters
     backend: str = "auto"              # auto | device | proxy | cpu
-    nvls: str = "off"                  # NVLink multicast object: off | on | auto
+    nvls: str = "auto"                 # NVLink multicast object: off | on | auto (on where every PE supports it)
     heap_mode: str = "auto"            # auto | vmm | ipc (how peers' heaps get mapped)
     proxy_slots: int = 1024            # ring slots of the reverse-offload queue
-    coll_ctas: int = 64                # CTAs per PE for host-launched collectives
+    coll_ctas: int = 128               # CTAs per PE for host-launched collectives
     slab_bytes: int = 1 << 20          # device-callable slab allocator region
 
     _ALIASES = {

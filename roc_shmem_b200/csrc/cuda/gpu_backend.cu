@@ -23,11 +23,13 @@
 #include "../host/runtime.h"
 #include "../include/bshmem_coll.cuh"
 #include "../include/bshmem_gpu.h"
+#include "coll_kernels.h"
 #include "gpu_heap.h"
 
 using namespace bshmem;
 using dev::State;
 using DTeam = bshmem::dev::Team;
+using collk::CollArgs;
 
 namespace {
 
@@ -98,6 +100,19 @@ __global__ void k_signal(State s, int pe, uint64_t sig_off, uint64_t value, int 
   else asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(sig), "l"(value) : "memory");
 }
 
+// Large messages: each CTA moves its share with bulk async copies through a shared-memory ring (no payload in
+// registers; see dev::bulk_copy_block).  `src` / `dst` are already translated to the peer mapping.
+constexpr int kBulkStages = 4, kBulkChunk = 32768;
+__global__ void __launch_bounds__(128) k_rma_bulk(State s, char* dst, const char* src, uint64_t n, int* status) {
+  extern __shared__ __align__(128) char bulk_smem[];
+  __shared__ __align__(8) uint64_t bars[kBulkStages];
+  uint64_t per = ((n + gridDim.x - 1) / gridDim.x + 127) & ~127ull;
+  uint64_t b = per * blockIdx.x, e = b + per < n ? b + per : n;
+  if (b >= n) return;
+  int rc = dev::bulk_copy_block<kBulkStages, kBulkChunk>(s, dst + b, src + b, e - b, bulk_smem, bars);
+  if (rc != BSHMEM_OK && threadIdx.x == 0) atomicCAS(status, 0, rc);
+}
+
 // Device-initiated put / get of a large message striped over the grid (block scope per CTA).
 __global__ void __launch_bounds__(1024) k_rma(State s, int pe, uint64_t sym_off, char* local, uint64_t n, int is_put, int scope) {
   uint64_t per = ((n + gridDim.x - 1) / gridDim.x + 15) & ~15ull;
@@ -127,96 +142,35 @@ __global__ void __launch_bounds__(1024) k_rma(State s, int pe, uint64_t sym_off,
   }
 }
 
-struct CollArgs {
-  int kind;            // BSHMEM_COLL_*
-  int dtype, op, root;
-  uint64_t dst_off, src_off, n;   // n: elements for reductions, bytes otherwise
-  uint64_t psync_off;  // active set
-  int use_nvls;
-  unsigned long long ll_epoch;   // != 0: epoch of a host-launched low-latency allreduce (same on every PE)
-};
-
-template <typename T>
-__device__ int reduce_typed(const State& s, const DTeam& t, const CollArgs& a, int cta, int ncta) {
-  T* d = reinterpret_cast<T*>(s.heap_base[s.my_pe] + a.dst_off);
-  const T* src = reinterpret_cast<const T*>(s.heap_base[s.my_pe] + a.src_off);
-  if (a.kind == BSHMEM_COLL_REDUCE_SCATTER) return coll::team_reduce_scatter<T>(s, t, a.op, d, src, a.n, cta, ncta);
-  if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value) {
-    // the multicast mapping spans every PE, so the in-switch reduction only fits a team that is the whole world
-    if (a.use_nvls && s.mc_base && t.size == s.n_pes && a.op == BSHMEM_SUM && ((a.dst_off | a.src_off) & 15) == 0 &&
-        (a.n * sizeof(T)) % 16 == 0)
-      return coll::team_reduce_nvls<T>(s, t, d, src, a.n, cta, ncta);
-  }
-  return coll::team_reduce<T>(s, t, a.op, d, src, a.n, cta, ncta, a.ll_epoch);
-}
-
-__device__ int run_coll(const State& s, DTeam t, const CollArgs& a, int cta, int ncta) {
-  char* base = s.heap_base[s.my_pe];
-  if (t.slot < 0) t.psync = reinterpret_cast<long*>(base + a.psync_off);
-  switch (a.kind) {
-    case BSHMEM_COLL_SYNC: return coll::team_sync(s, t, cta);
-    case BSHMEM_COLL_BARRIER: return coll::team_barrier(s, t, cta);
-    case BSHMEM_COLL_BROADCAST: return coll::team_broadcast(s, t, base + a.dst_off, base + a.src_off, a.n, a.root, cta, ncta);
-    case BSHMEM_COLL_FCOLLECT: return coll::team_fcollect(s, t, base + a.dst_off, base + a.src_off, a.n, cta, ncta);
-    case BSHMEM_COLL_ALLTOALL: return coll::team_alltoall(s, t, base + a.dst_off, base + a.src_off, a.n, cta, ncta);
-    case BSHMEM_COLL_REDUCE: case BSHMEM_COLL_REDUCE_SCATTER:
-      switch (a.dtype) {
-        case BSHMEM_INT8: return reduce_typed<int8_t>(s, t, a, cta, ncta);
-        case BSHMEM_UINT8: return reduce_typed<uint8_t>(s, t, a, cta, ncta);
-        case BSHMEM_INT16: return reduce_typed<int16_t>(s, t, a, cta, ncta);
-        case BSHMEM_UINT16: return reduce_typed<uint16_t>(s, t, a, cta, ncta);
-        case BSHMEM_INT32: return reduce_typed<int32_t>(s, t, a, cta, ncta);
-        case BSHMEM_UINT32: return reduce_typed<uint32_t>(s, t, a, cta, ncta);
-        case BSHMEM_INT64: return reduce_typed<long long>(s, t, a, cta, ncta);
-        case BSHMEM_UINT64: return reduce_typed<unsigned long long>(s, t, a, cta, ncta);
-        case BSHMEM_FLOAT: return reduce_typed<float>(s, t, a, cta, ncta);
-        case BSHMEM_DOUBLE: return reduce_typed<double>(s, t, a, cta, ncta);
-        case BSHMEM_BF16: return reduce_typed<__nv_bfloat16>(s, t, a, cta, ncta);
-        case BSHMEM_FP16: return reduce_typed<__half>(s, t, a, cta, ncta);
-      }
-      return BSHMEM_ERR_UNSUPPORTED;
-    case BSHMEM_COLL_EXCHANGE: {
-      // publish one u64 (held in a.n) in every member's exchange row, sync, leave the row for the host
-      if (threadIdx.x < t.size) {
-        uint64_t* row = reinterpret_cast<uint64_t*>(s.heap_base[dev::team_pe(t, threadIdx.x)] + BSHMEM_OFF_XCHG) +
-                        (size_t)t.slot * BSHMEM_MAX_PES;
-        row[t.my_idx] = a.n;
-      }
-      int rc = coll::team_barrier(s, t, cta);
-      if (rc != BSHMEM_OK) return rc;
-      return coll::team_sync(s, t, cta);   // nobody overwrites a row that is still being read... by the next exchange
-    }
-  }
-  return BSHMEM_ERR_INVALID;
-}
-
-__global__ void __launch_bounds__(512) k_coll(State s, DTeam t, CollArgs a, int* status) {
-  int rc = run_coll(s, t, a, blockIdx.x, gridDim.x);
-  if (rc != BSHMEM_OK && threadIdx.x == 0) atomicCAS(status, 0, rc);
-}
-
-// All PEs of a local group in ONE cooperative launch: blockIdx.y is the PE.  Used to exercise
-// the multi-PE algorithms on a single GPU (kernels that wait on one another must not be
-// separate launches on one device).
-__global__ void __launch_bounds__(512) k_coll_group(const State* states, const DTeam* teams, CollArgs a, int* status) {
-  State s = states[blockIdx.y];
-  DTeam t = teams[blockIdx.y];
-  if (t.my_idx < 0) return;
-  int rc = run_coll(s, t, a, blockIdx.x, gridDim.x);
-  if (rc != BSHMEM_OK && threadIdx.x == 0) atomicCAS(status, 0, rc);
-}
-
 // ---------------------------------------------------------------------------------
 // Backend
 // ---------------------------------------------------------------------------------
 #define RT_TRY(call) do { cudaError_t _e = (call); if (_e != cudaSuccess) return cuda_fail(#call, _e); } while (0)
 
+constexpr int kResultSlots = 64;
 struct Pinned {
-  bshmem_error_record_t err;
-  uint64_t amo_result;
-  int status;
-  uint64_t xchg[BSHMEM_MAX_PES];
+  bshmem_error_record_t err;       // lane 0's copy is the device-visible error record of the PE
+  uint64_t amo_result[kResultSlots];
+  int status[kResultSlots];
 };
+
+// What a host context owns on this backend: its ordering domain (a stream) and the pinned words its blocking calls
+// read results from.  Lane 0 is the default context; its stream is the settable PE stream.  Result words are handed
+// out round-robin per call, so threads that share a context do not read each other's answers.
+struct Lane {
+  cudaStream_t stream = nullptr;
+  Pinned* pinned = nullptr;
+  int* dstatus = nullptr;          // device status word of collectives launched on this lane
+  std::atomic<unsigned> next{0};
+  bool open = false;
+};
+
+// Selection of the calling thread (see Backend::ctx_select) and an optional binding of the thread to one lane for
+// everything it issues, collectives included (the reverse-offload service thread runs on a lane of its own).
+thread_local int tl_selected_ctx = 0;
+thread_local const void* tl_bound_backend = nullptr;
+thread_local int tl_bound_ctx = -1;
+thread_local std::string tl_err;
 
 class GpuBackend final : public Backend {
  public:
@@ -228,11 +182,14 @@ class GpuBackend final : public Backend {
     stream_ = own_stream_;
     RT_TRY(cudaHostAlloc(&pinned_, sizeof(Pinned), cudaHostAllocMapped));
     memset(pinned_, 0, sizeof(Pinned));
+    lanes_[0].pinned = pinned_;
+    lanes_[0].open = true;
     // counters followed by the (initially disabled) event ring
     RT_TRY(cudaMalloc(&dstats_, sizeof(unsigned long long) * (BSHMEM_DSTAT_COUNT + BSHMEM_TRACE_WORDS)));
     RT_TRY(cudaMemset(dstats_, 0, sizeof(unsigned long long) * (BSHMEM_DSTAT_COUNT + BSHMEM_TRACE_WORDS)));
     RT_TRY(cudaMalloc(&dstatus_, sizeof(int)));
     RT_TRY(cudaMemset(dstatus_, 0, sizeof(int)));
+    lanes_[0].dstatus = dstatus_;
     memset(&state_, 0, sizeof(state_));
     state_.my_pe = heap_->my_pe;
     state_.n_pes = heap_->n_pes;
@@ -253,6 +210,7 @@ class GpuBackend final : public Backend {
   ~GpuBackend() override {
     cudaSetDevice(heap_->device);
     cudaDeviceSynchronize();
+    for (int i = 1; i < BSHMEM_MAX_CTXS; ++i) ctx_close(i);
     if (own_stream_) cudaStreamDestroy(own_stream_);
     if (dstats_) cudaFree(dstats_);
     if (dstatus_) cudaFree(dstatus_);
@@ -269,7 +227,47 @@ class GpuBackend final : public Backend {
   char* peer_base(int pe) const override { return heap_->mapped[pe] ? heap_->base[pe] : nullptr; }
   bool host_dereferenceable() const override { return false; }
   void set_timeout_us(uint64_t t) override { state_.timeout_ns = t * 1000ull; }
-  std::string last_error() const override { return err_; }
+  std::string last_error() const override { return tl_err; }
+
+  // ---- host contexts -----------------------------------------------------------------
+  int ctx_open(int idx, long) override {
+    if (idx <= 0 || idx >= BSHMEM_MAX_CTXS) return BSHMEM_ERR_INVALID;
+    Lane& L = lanes_[idx];
+    if (L.open) return BSHMEM_OK;
+    RT_TRY(cudaSetDevice(heap_->device));
+    RT_TRY(cudaStreamCreateWithFlags(&L.stream, cudaStreamNonBlocking));
+    RT_TRY(cudaHostAlloc(&L.pinned, sizeof(Pinned), cudaHostAllocMapped));
+    memset(L.pinned, 0, sizeof(Pinned));
+    RT_TRY(cudaMalloc(&L.dstatus, sizeof(int)));
+    RT_TRY(cudaMemset(L.dstatus, 0, sizeof(int)));
+    L.open = true;
+    return BSHMEM_OK;
+  }
+  void ctx_close(int idx) override {
+    if (idx <= 0 || idx >= BSHMEM_MAX_CTXS || !lanes_[idx].open) return;
+    Lane& L = lanes_[idx];
+    L.open = false;
+    if (L.stream) { cudaStreamSynchronize(L.stream); cudaStreamDestroy(L.stream); L.stream = nullptr; }
+    if (L.pinned) { cudaFreeHost(L.pinned); L.pinned = nullptr; }
+    if (L.dstatus) { cudaFree(L.dstatus); L.dstatus = nullptr; }
+  }
+  void ctx_select(int idx) override { tl_selected_ctx = idx; }
+  // Everything the calling thread issues from now on (collectives too) runs on context idx's lane; -1 unbinds.
+  int bind_thread(int idx) {
+    if (idx >= 0 && (idx >= BSHMEM_MAX_CTXS || !lanes_[idx].open)) return BSHMEM_ERR_INVALID;
+    tl_bound_backend = idx >= 0 ? this : nullptr;
+    tl_bound_ctx = idx;
+    return BSHMEM_OK;
+  }
+  bool thread_is_bound() const { return tl_bound_backend == this && tl_bound_ctx >= 0; }
+  Lane& lane() {
+    int i = thread_is_bound() ? tl_bound_ctx : tl_selected_ctx;
+    if (i < 0 || i >= BSHMEM_MAX_CTXS || !lanes_[i].open) i = 0;
+    return lanes_[i];
+  }
+  // Collectives belong to no context: they run on the PE stream unless the thread is bound to a lane.
+  Lane& coll_lane() { return thread_is_bound() ? lanes_[tl_bound_ctx] : lanes_[0]; }
+  cudaStream_t stream_of(const Lane& L) const { return &L == &lanes_[0] ? stream_ : L.stream; }
 
   bshmem_error_record_t last_record(bool clear) override {
     bshmem_error_record_t r = pinned_->err;
@@ -289,16 +287,19 @@ class GpuBackend final : public Backend {
   unsigned long long* dstats() const { return dstats_; }
   void refresh_mc() { state_.mc_base = heap_->mc_base; }
 
-  int finish(const char* what) {
-    if (!blocking_) return BSHMEM_OK;
-    RT_TRY(cudaStreamSynchronize(stream_));
+  // a thread bound to a lane (the reverse-offload service thread) always completes what it issues: the device
+  // producer that waits for its answer cannot synchronise a host stream
+  bool blocking_now() const { return blocking_ || thread_is_bound(); }
+  int finish(const char* what, cudaStream_t st) {
+    if (!blocking_now()) return BSHMEM_OK;
+    RT_TRY(cudaStreamSynchronize(st));
     return check_device_error(what);
   }
 
   int check_device_error(const char* what) {
     if (pinned_->err.code != 0) {
       int code = (int)pinned_->err.code;
-      err_ = std::string(what) + ": device-side " + bshmem_status_string(code) + " at site " +
+      tl_err = std::string(what) + ": device-side " + bshmem_status_string(code) + " at site " +
              std::to_string(pinned_->err.where) + " waiting for pe " + std::to_string(pinned_->err.pe);
       return code;
     }
@@ -307,30 +308,36 @@ class GpuBackend final : public Backend {
 
   // ---- RMA ------------------------------------------------------------------------
   int put(int pe, uint64_t dst_off, const void* local, uint64_t n, bool nbi) override {
-    RT_TRY(cudaMemcpyAsync(heap_->base[pe] + dst_off, local, n, cudaMemcpyDefault, stream_));
+    const cudaStream_t st = stream_of(lane());
+    RT_TRY(cudaMemcpyAsync(heap_->base[pe] + dst_off, local, n, cudaMemcpyDefault, st));
     if (nbi) return BSHMEM_OK;
-    return finish("put");
+    return finish("put", st);
   }
   int get(int pe, void* local, uint64_t src_off, uint64_t n, bool nbi) override {
-    RT_TRY(cudaMemcpyAsync(local, heap_->base[pe] + src_off, n, cudaMemcpyDefault, stream_));
+    const cudaStream_t st = stream_of(lane());
+    RT_TRY(cudaMemcpyAsync(local, heap_->base[pe] + src_off, n, cudaMemcpyDefault, st));
     if (nbi) return BSHMEM_OK;
-    return finish("get");
+    return finish("get", st);
   }
   int put_signal(int pe, uint64_t dst_off, const void* local, uint64_t n, uint64_t sig_off, uint64_t sig_val, int sig_op,
                  bool nbi) override {
-    if (n) RT_TRY(cudaMemcpyAsync(heap_->base[pe] + dst_off, local, n, cudaMemcpyDefault, stream_));
-    k_signal<<<1, 1, 0, stream_>>>(state_, pe, sig_off, sig_val, sig_op);
+    const cudaStream_t st = stream_of(lane());
+    if (n) RT_TRY(cudaMemcpyAsync(heap_->base[pe] + dst_off, local, n, cudaMemcpyDefault, st));
+    k_signal<<<1, 1, 0, st>>>(state_, pe, sig_off, sig_val, sig_op);
     RT_TRY(cudaGetLastError());
     if (nbi) return BSHMEM_OK;
-    return finish("put_signal");
+    return finish("put_signal", st);
   }
   int amo(int pe, uint64_t off, int dtype, int op, uint64_t value, uint64_t cond, uint64_t* fetched) override {
-    k_amo<<<1, 1, 0, stream_>>>(state_, pe, off, dtype, op, value, cond, &pinned_->amo_result);
+    Lane& L = lane();
+    const cudaStream_t st = stream_of(L);
+    uint64_t* slot = &L.pinned->amo_result[L.next.fetch_add(1, std::memory_order_relaxed) % kResultSlots];
+    k_amo<<<1, 1, 0, st>>>(state_, pe, off, dtype, op, value, cond, slot);
     RT_TRY(cudaGetLastError());
     bool fetching = op <= BSHMEM_AMO_FETCH_CSWAP || op == BSHMEM_AMO_SWAP || (op >= BSHMEM_AMO_FETCH_AND && op <= BSHMEM_AMO_FETCH_XOR);
-    if (fetching || blocking_) {
-      RT_TRY(cudaStreamSynchronize(stream_));
-      if (fetched) *fetched = pinned_->amo_result;
+    if (fetching || blocking_now()) {
+      RT_TRY(cudaStreamSynchronize(st));
+      if (fetched) *fetched = *slot;
     }
     return BSHMEM_OK;
   }
@@ -339,20 +346,23 @@ class GpuBackend final : public Backend {
     // Stream mode: operations of the PE's stream complete in order, and whatever the caller
     // enqueues next on that stream runs after them, so there is nothing to wait for on the
     // host; bshmem_gpu_synchronize() is the explicit host-side wait.
-    if (!blocking_) return BSHMEM_OK;
-    RT_TRY(cudaStreamSynchronize(stream_));
+    if (!blocking_now()) return BSHMEM_OK;
+    RT_TRY(cudaStreamSynchronize(stream_of(lane())));     // this context's operations only
     return check_device_error("quiet");
   }
   int wait_until(uint64_t off, int dtype, int cmp, uint64_t value, uint64_t timeout_us) override {
     State s = state_;
     s.timeout_ns = timeout_us * 1000ull;
-    pinned_->status = 0;
-    k_wait_until<<<1, 1, 0, stream_>>>(s, off, dtype, cmp, value, &pinned_->status);
+    Lane& L = lane();
+    const cudaStream_t st = stream_of(L);
+    int* slot = &L.pinned->status[L.next.fetch_add(1, std::memory_order_relaxed) % kResultSlots];
+    *slot = 0;
+    k_wait_until<<<1, 1, 0, st>>>(s, off, dtype, cmp, value, slot);
     RT_TRY(cudaGetLastError());
-    if (!blocking_) return BSHMEM_OK;
-    RT_TRY(cudaStreamSynchronize(stream_));
-    int rc = pinned_->status;
-    if (rc != BSHMEM_OK) err_ = "wait_until: device-side timeout";
+    if (!blocking_now()) return BSHMEM_OK;
+    RT_TRY(cudaStreamSynchronize(st));
+    int rc = *slot;
+    if (rc != BSHMEM_OK) tl_err = "wait_until: device-side timeout";
     return rc;
   }
   int test(uint64_t off, int dtype, int cmp, uint64_t value, int* result) override {
@@ -360,11 +370,14 @@ class GpuBackend final : public Backend {
     s.timeout_ns = 0;   // a wait that gives up at once is a test
     s.err = nullptr;
     s.stats = nullptr;
-    pinned_->status = 0;
-    k_wait_until<<<1, 1, 0, stream_>>>(s, off, dtype, cmp, value, &pinned_->status);
+    Lane& L = lane();
+    const cudaStream_t st = stream_of(L);
+    int* slot = &L.pinned->status[L.next.fetch_add(1, std::memory_order_relaxed) % kResultSlots];
+    *slot = 0;
+    k_wait_until<<<1, 1, 0, st>>>(s, off, dtype, cmp, value, slot);
     RT_TRY(cudaGetLastError());
-    RT_TRY(cudaStreamSynchronize(stream_));
-    *result = pinned_->status == BSHMEM_OK ? 1 : 0;
+    RT_TRY(cudaStreamSynchronize(st));
+    *result = *slot == BSHMEM_OK ? 1 : 0;
     return BSHMEM_OK;
   }
 
@@ -382,7 +395,7 @@ class GpuBackend final : public Backend {
       // exist.  Host syncs are no-ops (the caller owns ordering); data collectives go through
       // bshmem_gpu_group_collective, which runs all PEs in one cooperative launch.
       if (a.kind == BSHMEM_COLL_SYNC || a.kind == BSHMEM_COLL_BARRIER) return BSHMEM_OK;
-      err_ = std::string(what) + ": use the group collective entry for a local group";
+      tl_err = std::string(what) + ": use the group collective entry for a local group";
       return BSHMEM_ERR_UNSUPPORTED;
     }
     a.psync_off = g.psync_off;
@@ -392,9 +405,12 @@ class GpuBackend final : public Backend {
       ctas = (int)((bytes + (32u << 10) - 1) / (32u << 10));
       if (ctas > coll_ctas_) ctas = coll_ctas_;
     }
+    Lane& L = coll_lane();
+    const cudaStream_t st = stream_of(L);
+    const bool main_lane = &L == &lanes_[0];   // the slot / staging fast paths count calls per PE, so only the PE stream takes them
     a.ll_epoch = 0;
     const uint64_t unit = bshmem_dtype_size(a.dtype) > 4 ? bshmem_dtype_size(a.dtype) : 4;
-    if (a.kind == BSHMEM_COLL_REDUCE && g.slot == 0 && g.set.size == heap_->n_pes && !use_nvls_ &&
+    if (main_lane && a.kind == BSHMEM_COLL_REDUCE && g.slot == 0 && g.set.size == heap_->n_pes &&
         bytes > BSHMEM_LL_PAYLOAD_BYTES && bytes <= BSHMEM_LLB_PAYLOAD_BYTES && bytes % unit == 0 &&
         ((a.dst_off | a.src_off) & (unit - 1)) == 0) {
       // mid-size allreduce on the world team: one exchange through the per-sender slots.  The conditions are exactly
@@ -404,17 +420,34 @@ class GpuBackend final : public Backend {
       ctas = (int)((bytes + (8u << 10) - 1) / (8u << 10));      // 8 KiB of payload per block
       if (ctas > coll_ctas_) ctas = coll_ctas_;
     }
-    k_coll<<<ctas, 512, 0, stream_>>>(state_, team_of(g), a, dstatus_);
-    RT_TRY(cudaGetLastError());
-    if (!blocking_) return BSHMEM_OK;
-    RT_TRY(cudaStreamSynchronize(stream_));
-    int st = 0;
-    RT_TRY(cudaMemcpy(&st, dstatus_, sizeof(int), cudaMemcpyDeviceToHost));
-    if (st != 0) {
-      cudaMemset(dstatus_, 0, sizeof(int));
+    // One exchange through the staging region instead of sync + work + barrier: world team, what a PE receives fits a
+    // staging half, 16-byte granular.  Every PE evaluates the same conditions on the same arguments, so the call
+    // number (and with it the staging half) is the same everywhere.
+    a.stage_seq = 0;
+    if (main_lane && g.slot == 0 && g.set.size == heap_->n_pes && heap_->n_pes > 1 && a.ll_epoch == 0 && bytes >= 16 &&
+        bytes + 4096 <= BSHMEM_STAGE_BYTES && ((a.dst_off | a.src_off) & 15) == 0) {
+      const uint64_t es = bshmem_dtype_size(a.dtype);
+      bool fits = false;
+      switch (a.kind) {
+        case BSHMEM_COLL_FCOLLECT: case BSHMEM_COLL_ALLTOALL: fits = a.n % 16 == 0; break;
+        case BSHMEM_COLL_REDUCE_SCATTER: fits = (a.n * es) % 16 == 0; break;
+        // the multicast reduction needs no staging; below the one-shot limit the pull form is a single pass
+        case BSHMEM_COLL_REDUCE: fits = !(use_nvls_ && a.op == BSHMEM_SUM && (a.dtype == BSHMEM_FLOAT || a.dtype == BSHMEM_BF16)) &&
+                                        bytes > BSHMEM_LLB_PAYLOAD_BYTES; break;
+        default: break;
+      }
+      if (fits) a.stage_seq = ++stage_seq_;
+    }
+    RT_TRY(collk::launch(state_, team_of(g), a, ctas, L.dstatus, st));
+    if (!blocking_now()) return BSHMEM_OK;
+    int rc = 0;
+    RT_TRY(cudaMemcpyAsync(&rc, L.dstatus, sizeof(int), cudaMemcpyDeviceToHost, st));
+    RT_TRY(cudaStreamSynchronize(st));
+    if (rc != 0) {
+      cudaMemsetAsync(L.dstatus, 0, sizeof(int), st);
       check_device_error(what);
-      if (err_.empty()) err_ = std::string(what) + " failed on the device";
-      return st;
+      if (tl_err.empty()) tl_err = std::string(what) + " failed on the device";
+      return rc;
     }
     return BSHMEM_OK;
   }
@@ -477,7 +510,7 @@ class GpuBackend final : public Backend {
   }
 
   int cuda_fail(const char* what, cudaError_t e) {
-    err_ = std::string(what) + ": " + cudaGetErrorString(e);
+    tl_err = std::string(what) + ": " + cudaGetErrorString(e);
     return BSHMEM_ERR_CUDA;
   }
 
@@ -494,8 +527,9 @@ class GpuBackend final : public Backend {
   bool blocking_ = true;
   bool use_nvls_ = false;
   int coll_ctas_ = 32;
+  Lane lanes_[BSHMEM_MAX_CTXS];
   unsigned long long ll_epoch_ = 0;     // epochs of host-launched low-latency allreduces
-  std::string err_;
+  unsigned long long stage_seq_ = 0;    // call numbers of staged one-exchange collectives
 };
 
 GpuBackend* gpu_of(bshmem_handle_t h) {
@@ -554,8 +588,8 @@ int bshmem_gpu_init(void* heap, const bshmem_config_t* cfg, int coll_ctas, int o
     cudaFuncGetAttributes(&fa, k_wait_until);
     cudaFuncGetAttributes(&fa, k_signal);
     cudaFuncGetAttributes(&fa, k_rma);
-    cudaFuncGetAttributes(&fa, k_coll);
-    cudaFuncGetAttributes(&fa, k_coll_group);
+    cudaFuncGetAttributes(&fa, k_rma_bulk);
+    collk::preload();
   }
   if (rc != BSHMEM_OK) { g_err = be->last_error(); delete be; return rc; }
   *out = make_runtime(std::unique_ptr<Backend>(be), &c);
@@ -566,6 +600,20 @@ int bshmem_gpu_set_stream(bshmem_handle_t h, void* stream) {
   GpuBackend* g = gpu_of(h);
   if (!g) return BSHMEM_ERR_STATE;
   g->set_stream(static_cast<cudaStream_t>(stream));
+  return BSHMEM_OK;
+}
+// Binds the calling thread to host context `ctx` of this PE: everything the thread issues from now on, collectives
+// included, runs on that context's stream and completes before the call returns; ctx < 0 unbinds.  The
+// reverse-offload service thread uses this so that its work never queues behind the kernel that waits for it.
+int bshmem_gpu_bind_thread_ctx(bshmem_handle_t h, int ctx) {
+  GpuBackend* g = gpu_of(h);
+  if (!g) return BSHMEM_ERR_STATE;
+  return g->bind_thread(ctx);
+}
+int bshmem_gpu_get_device(bshmem_handle_t h, int* device) {
+  GpuBackend* g = gpu_of(h);
+  if (!g || !device) return BSHMEM_ERR_STATE;
+  *device = g->heap()->device;
   return BSHMEM_OK;
 }
 int bshmem_gpu_get_stream(bshmem_handle_t h, void** stream) {
@@ -671,7 +719,23 @@ int bshmem_gpu_rma_kernel(bshmem_handle_t h, void* sym, void* local, uint64_t n,
   if (ctas < 1) ctas = 1;
   if (threads < 32) threads = 32;
   if (threads > 1024) threads = 1024;
-  k_rma<<<ctas, threads, 0, g->stream()>>>(g->state(), pe, off, static_cast<char*>(local), n, is_put, scope);
+  // scope 3 = bulk async copies through shared memory
+  const bool aligned = ((reinterpret_cast<uintptr_t>(local) | off | n) & 15) == 0;
+  if (scope == 3 && !aligned) return BSHMEM_ERR_INVALID;
+  if (scope == 3) {
+    static bool attr_set[64] = {};
+    const int d = g->heap()->device;
+    if (d >= 0 && d < 64 && !attr_set[d]) {
+      cudaFuncSetAttribute(k_rma_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkStages * kBulkChunk);
+      attr_set[d] = true;
+    }
+    char* remote = g->heap()->base[pe] + off;
+    char* loc = static_cast<char*>(local);
+    k_rma_bulk<<<ctas, 128, kBulkStages * kBulkChunk, g->stream()>>>(g->state(), is_put ? remote : loc, is_put ? loc : remote, n,
+                                                                     g->dstatus());
+  } else {
+    k_rma<<<ctas, threads, 0, g->stream()>>>(g->state(), pe, off, static_cast<char*>(local), n, is_put, scope);
+  }
   cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) {
     g_err = std::string("rma kernel launch: ") + cudaGetErrorString(ce);
@@ -698,6 +762,14 @@ int bshmem_gpu_group_collective(bshmem_handle_t* handles, int n, int team_slot, 
     if (handles[i]->group_of_team(team_slot, &cg) == BSHMEM_OK) ht[i] = g->team_of(cg);
     else { memset(&ht[i], 0, sizeof(DTeam)); ht[i].my_idx = -1; }
   }
+  if (ctas > BSHMEM_MAX_COLL_CTAS) ctas = BSHMEM_MAX_COLL_CTAS;     // one flag row per channel exists, no more
+  for (int i = 0; i < n; ++i) {
+    if (ht[i].my_idx < 0) continue;
+    uint64_t sb = 0, db = 0;
+    collk::extent(kind, dtype, count, ht[i].size, &sb, &db);
+    if (src_off > hs[i].heap_bytes || sb > hs[i].heap_bytes - src_off || dst_off > hs[i].heap_bytes || db > hs[i].heap_bytes - dst_off)
+      return BSHMEM_ERR_RANGE;
+  }
   State* ds = nullptr;
   DTeam* dt = nullptr;
   if (cudaMalloc(&ds, sizeof(State) * n) != cudaSuccess || cudaMalloc(&dt, sizeof(DTeam) * n) != cudaSuccess) return BSHMEM_ERR_CUDA;
@@ -707,8 +779,7 @@ int bshmem_gpu_group_collective(bshmem_handle_t* handles, int n, int team_slot, 
   a.kind = kind; a.dtype = dtype; a.op = op; a.root = root; a.dst_off = dst_off; a.src_off = src_off; a.n = count;
   int* status = g0->dstatus();
   if (ctas < 1) ctas = 1;
-  void* args[] = {&ds, &dt, &a, &status};
-  cudaError_t e = cudaLaunchCooperativeKernel((void*)k_coll_group, dim3(ctas, n), dim3(512), args, 0, g0->stream());
+  cudaError_t e = collk::launch_group(ds, dt, a, ctas, n, status, g0->stream());
   int rc = BSHMEM_OK;
   if (e != cudaSuccess) { g_err = std::string("cooperative launch: ") + cudaGetErrorString(e); rc = BSHMEM_ERR_CUDA; }
   else if (cudaStreamSynchronize(g0->stream()) != cudaSuccess) rc = BSHMEM_ERR_CUDA;

@@ -1,6 +1,6 @@
 // gpu_proxy.cu — reverse-offload mode on the GPU backend: the command ring lives in pinned,
 // device-mapped host memory, the ticket counter in device memory, and the service thread
-// executes descriptors through a second runtime handle on the same heap (its own CUDA
+// executes descriptors through the PE's runtime on a host context of its own (its own CUDA
 // stream, so host work for the proxy never queues behind the kernel that is waiting for it).
 //
 // Parity: library/src/reverse_offload/backend_ro.cpp:47-109 (ROBackend wiring: queues in
@@ -22,16 +22,25 @@ using dev::State;
 
 namespace {
 
+// Executes descriptors through the PE's own runtime, on a host context of its own: the service thread binds itself
+// to that context, so everything it issues (RMA, atomics and team collectives alike) runs on the context's stream,
+// never behind the kernel on the PE stream that is waiting for the answer, and teams created on the PE are known.
 class GpuExecutor final : public ProxyExecutor {
  public:
   GpuExecutor(bshmem_handle_t h, int device) : inner_(h), h_(h), device_(device) {}
-  ~GpuExecutor() override { bshmem_finalize(h_); }
-  void thread_init() override { cudaSetDevice(device_); }
+  ~GpuExecutor() override {
+    if (ctx_ > 0) bshmem_ctx_destroy(h_, ctx_);
+  }
+  void thread_init() override {
+    cudaSetDevice(device_);
+    if (bshmem_ctx_create(h_, BSHMEM_CTX_ZERO, &ctx_) == BSHMEM_OK) bshmem_gpu_bind_thread_ctx(h_, ctx_);
+  }
   int execute(const bshmem_proxy_desc_t& d, uint64_t* result) override { return inner_.execute(d, result); }
  private:
   RuntimeExecutor inner_;
   bshmem_handle_t h_;
   int device_;
+  bshmem_ctx_t ctx_ = BSHMEM_CTX_INVALID;
 };
 
 thread_local std::string g_err;
@@ -92,15 +101,9 @@ int bshmem_gpu_proxy_create(void* heap, bshmem_handle_t main, uint64_t capacity,
                             void** handle_out, void** ring_dev_out, bshmem_proxy_t** px_out) {
   if (!heap || !main || !handle_out || capacity < 2 || (capacity & (capacity - 1))) return BSHMEM_ERR_INVALID;
   if (cudaSetDevice(device) != cudaSuccess) { g_err = "cudaSetDevice failed"; return BSHMEM_ERR_CUDA; }
-  // second runtime handle on the same heap: own stream, own pinned result slots
-  bshmem_config_t cfg = main->cfg;
-  bshmem_handle_t worker = nullptr;
-  int rc = bshmem_gpu_init(heap, &cfg, 8, /*own_heap=*/0, &worker);
-  if (rc != BSHMEM_OK) { g_err = std::string("proxy worker runtime: ") + bshmem_gpu_last_error(); return rc; }
   uint64_t bytes = proxy_ring_bytes(capacity);
   void* pinned = nullptr;
   if (cudaHostAlloc(&pinned, bytes, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
-    bshmem_finalize(worker);
     g_err = "cudaHostAlloc(ring) failed";
     return BSHMEM_ERR_CUDA;
   }
@@ -113,7 +116,7 @@ int bshmem_gpu_proxy_create(void* heap, bshmem_handle_t main, uint64_t capacity,
     return BSHMEM_ERR_CUDA;
   }
   bshmem_proxy* px = proxy_start(pinned, capacity, widx, timeout_us * 1000ull,
-                                 std::unique_ptr<ProxyExecutor>(new GpuExecutor(worker, device)));
+                                 std::unique_ptr<ProxyExecutor>(new GpuExecutor(main, device)));
   if (!px) { g_err = "proxy_start failed"; return BSHMEM_ERR_INVALID; }
   // with unified addressing the pinned host pointers are valid on the device as they are
   bshmem_proxy_ring_t ring = px->ring;

@@ -1,19 +1,21 @@
 // group_noalloc.cu — bshmem_gpu_group_collective_noalloc(): the group collective for
 // callers that must not allocate device memory.  See bshmem_gpu_noalloc.h for who those
 // callers are and for the limits; this file holds the fixed scratch array, its one-time
-// address look-up and the launch.
+// address look-up and the launch (of the same cooperative kernels the allocating entry runs,
+// coll_kernels.h, handed pointers into the array).
 #include <cuda_runtime.h>
 
 #include <cstring>
 #include <mutex>
 #include <string>
 
-#include "../include/bshmem_coll.cuh"
+#include "../include/bshmem_gpu.h"
 #include "../include/bshmem_gpu_noalloc.h"
+#include "coll_kernels.h"
 
 using namespace bshmem;
-using dev::State;
-using DTeam = bshmem::dev::Team;
+using State = bshmem_dev_state_t;
+using DTeam = bshmem_team_dev_t;
 
 namespace {
 
@@ -26,56 +28,6 @@ constexpr size_t kStatesBytes = sizeof(State) * BSHMEM_NOALLOC_MAX_PES;
 constexpr size_t kTeamsBytes = sizeof(DTeam) * BSHMEM_NOALLOC_MAX_PES;
 constexpr size_t kStatusOffset = kStatesBytes + kTeamsBytes;
 static_assert(kStatusOffset + sizeof(int) <= BSHMEM_NOALLOC_SCRATCH_BYTES, "scratch array too small for 16 PEs");
-
-struct Args {
-  int kind, dtype, op, root;
-  uint64_t dst_off, src_off, n;
-};
-
-template <typename T>
-__device__ int reduce_as(const State& s, const DTeam& t, const Args& a, int cta, int ncta) {
-  T* d = reinterpret_cast<T*>(s.heap_base[s.my_pe] + a.dst_off);
-  const T* src = reinterpret_cast<const T*>(s.heap_base[s.my_pe] + a.src_off);
-  if (a.kind == BSHMEM_COLL_REDUCE_SCATTER) return coll::team_reduce_scatter<T>(s, t, a.op, d, src, a.n, cta, ncta);
-  return coll::team_reduce<T>(s, t, a.op, d, src, a.n, cta, ncta);
-}
-
-__device__ int run_one(const State& s, const DTeam& t, const Args& a, int cta, int ncta) {
-  char* base = s.heap_base[s.my_pe];
-  switch (a.kind) {
-    case BSHMEM_COLL_SYNC: return coll::team_sync(s, t, cta);
-    case BSHMEM_COLL_BARRIER: return coll::team_barrier(s, t, cta);
-    case BSHMEM_COLL_BROADCAST: return coll::team_broadcast(s, t, base + a.dst_off, base + a.src_off, a.n, a.root, cta, ncta);
-    case BSHMEM_COLL_FCOLLECT: return coll::team_fcollect(s, t, base + a.dst_off, base + a.src_off, a.n, cta, ncta);
-    case BSHMEM_COLL_ALLTOALL: return coll::team_alltoall(s, t, base + a.dst_off, base + a.src_off, a.n, cta, ncta);
-    case BSHMEM_COLL_REDUCE: case BSHMEM_COLL_REDUCE_SCATTER:
-      switch (a.dtype) {
-        case BSHMEM_INT8: return reduce_as<int8_t>(s, t, a, cta, ncta);
-        case BSHMEM_UINT8: return reduce_as<uint8_t>(s, t, a, cta, ncta);
-        case BSHMEM_INT16: return reduce_as<int16_t>(s, t, a, cta, ncta);
-        case BSHMEM_UINT16: return reduce_as<uint16_t>(s, t, a, cta, ncta);
-        case BSHMEM_INT32: return reduce_as<int32_t>(s, t, a, cta, ncta);
-        case BSHMEM_UINT32: return reduce_as<uint32_t>(s, t, a, cta, ncta);
-        case BSHMEM_INT64: return reduce_as<long long>(s, t, a, cta, ncta);
-        case BSHMEM_UINT64: return reduce_as<unsigned long long>(s, t, a, cta, ncta);
-        case BSHMEM_FLOAT: return reduce_as<float>(s, t, a, cta, ncta);
-        case BSHMEM_DOUBLE: return reduce_as<double>(s, t, a, cta, ncta);
-        case BSHMEM_BF16: return reduce_as<__nv_bfloat16>(s, t, a, cta, ncta);
-        case BSHMEM_FP16: return reduce_as<__half>(s, t, a, cta, ncta);
-      }
-      return BSHMEM_ERR_UNSUPPORTED;
-  }
-  return BSHMEM_ERR_INVALID;
-}
-
-// Same shape as the allocating entry's kernel: one cooperative launch, blockIdx.y is the PE.
-__global__ void __launch_bounds__(512) k_group_static(const State* states, const DTeam* teams, Args a, int* status) {
-  State s = states[blockIdx.y];
-  DTeam t = teams[blockIdx.y];
-  if (t.my_idx < 0) return;
-  int rc = run_one(s, t, a, blockIdx.x, gridDim.x);
-  if (rc != BSHMEM_OK && threadIdx.x == 0) atomicCAS(status, 0, rc);
-}
 
 thread_local std::string g_err;
 std::mutex g_mu;
@@ -116,6 +68,17 @@ int bshmem_gpu_group_collective_noalloc(bshmem_handle_t* handles, int n, int tea
     return BSHMEM_ERR_LIMIT;
   }
   if (kind < BSHMEM_COLL_SYNC || kind > BSHMEM_COLL_ALLTOALL) { g_err = "unknown collective kind"; return BSHMEM_ERR_INVALID; }
+  // The array that is resolved and written below belongs to the CURRENT device, so that must be the handles' device.
+  int cur = -1, hdev = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess || bshmem_gpu_get_device(handles[0], &hdev) != BSHMEM_OK) {
+    g_err = "cannot determine the current device or the handles' device";
+    return BSHMEM_ERR_STATE;
+  }
+  if (cur != hdev) {
+    g_err = "the current CUDA device (" + std::to_string(cur) + ") is not the device of the group's heaps (" + std::to_string(hdev) +
+            "); call cudaSetDevice first";
+    return BSHMEM_ERR_STATE;
+  }
 
   // Host image of the scratch: states, teams, and a zero status word (the array keeps the
   // previous call's contents, so everything the kernel reads is rewritten here).
@@ -137,6 +100,15 @@ int bshmem_gpu_group_collective_noalloc(bshmem_handle_t* handles, int n, int tea
     t.pe_start = bshmem_team_translate_pe(handles[i], team_slot, 0, BSHMEM_TEAM_WORLD);
     t.stride = t.size > 1 ? bshmem_team_translate_pe(handles[i], team_slot, 1, BSHMEM_TEAM_WORLD) - t.pe_start : 1;
   }
+  for (int i = 0; i < n; ++i) {
+    if (ht[i].my_idx < 0) continue;
+    uint64_t sb = 0, db = 0;
+    collk::extent(kind, dtype, count, ht[i].size, &sb, &db);
+    if (src_off > hs[i].heap_bytes || sb > hs[i].heap_bytes - src_off || dst_off > hs[i].heap_bytes || db > hs[i].heap_bytes - dst_off) {
+      g_err = "source or destination range lies outside the symmetric heap";
+      return BSHMEM_ERR_RANGE;
+    }
+  }
   if (bshmem_gpu_get_stream(handles[0], &stream_v) != BSHMEM_OK) { g_err = "cannot get the PE's stream"; return BSHMEM_ERR_STATE; }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
@@ -149,16 +121,18 @@ int bshmem_gpu_group_collective_noalloc(bshmem_handle_t* handles, int n, int tea
   const State* d_states = reinterpret_cast<const State*>(scratch);
   const DTeam* d_teams = reinterpret_cast<const DTeam*>(scratch + kStatesBytes);
   int* d_status = reinterpret_cast<int*>(scratch + kStatusOffset);
-  Args a{kind, dtype, op, root, dst_off, src_off, count};
+  collk::CollArgs a{};
+  a.kind = kind; a.dtype = dtype; a.op = op; a.root = root; a.dst_off = dst_off; a.src_off = src_off; a.n = count;
   if (ctas < 1) ctas = 1;
-  void* args[] = {&d_states, &d_teams, &a, &d_status};
-  e = cudaLaunchCooperativeKernel((void*)k_group_static, dim3(ctas, n), dim3(512), args, 0, stream);
+  if (ctas > BSHMEM_MAX_COLL_CTAS) ctas = BSHMEM_MAX_COLL_CTAS;     // one flag row per channel exists, no more
+  e = collk::launch_group(d_states, d_teams, a, ctas, n, d_status, stream);
   if (e != cudaSuccess) { g_err = std::string("cooperative launch: ") + cudaGetErrorString(e); return BSHMEM_ERR_CUDA; }
+  // the status word comes back on the PE's own stream: nothing here touches any other stream of the device
+  int st = 0;
+  e = cudaMemcpyAsync(&st, d_status, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) { g_err = std::string("status read: ") + cudaGetErrorString(e); return BSHMEM_ERR_CUDA; }
   e = cudaStreamSynchronize(stream);
   if (e != cudaSuccess) { g_err = std::string("stream synchronize: ") + cudaGetErrorString(e); return BSHMEM_ERR_CUDA; }
-  int st = 0;
-  e = cudaMemcpy(&st, d_status, sizeof(int), cudaMemcpyDeviceToHost);
-  if (e != cudaSuccess) { g_err = std::string("status read: ") + cudaGetErrorString(e); return BSHMEM_ERR_CUDA; }
   if (st != 0) g_err = "a device-side wait of the collective ran out";
   return st;
 }

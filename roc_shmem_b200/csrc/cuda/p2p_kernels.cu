@@ -94,6 +94,28 @@ __global__ void k_put_msgrate(State s, char* dest, const char* src, size_t size,
   if (tid == 0) { out->ns = dt; out->status = BSHMEM_OK; }
 }
 
+// Every thread of the grid issues `iters` fetch-adds on one of `words` target words of the peer (thread t uses word
+// t % words): the rate of independent 8-byte atomics over NVLink as the number of issuing CTAs grows.
+__global__ void k_amo_rate(State s, unsigned long long* target, int words, int peer, int iters, BenchOut* out) {
+  size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  unsigned long long* t = target + tid % (size_t)words;
+  unsigned long long t0 = dev::timer(), acc = 0;
+  for (int i = 0; i < iters; ++i) acc += dev::atomic_fetch_add<unsigned long long>(s, t, 1ull, peer);
+  unsigned long long dt = dev::timer() - t0;
+  if (tid == 0) { out->ns = dt; out->status = (int)(acc & 0); }
+}
+
+// One-way putmem_signal stream: every CTA puts its share of `nbytes` and adds 1 to the signal word, `iters` times;
+// the target PE is not involved (its signal word just counts), so this measures put-with-signal bandwidth.
+__global__ void __launch_bounds__(1024) k_put_signal_stream(State s, char* data, const char* src, uint64_t* sig, size_t nbytes, int peer,
+                                                           int iters) {
+  size_t per = ((nbytes + gridDim.x - 1) / gridDim.x + 15) & ~(size_t)15;
+  size_t b = per * blockIdx.x, e = b + per < nbytes ? b + per : nbytes;
+  if (b >= nbytes) return;
+  for (int i = 0; i < iters; ++i)
+    dev::putmem_signal<dev::BLOCK>(s, data + b, src + b, e - b, sig, 1ull, BSHMEM_SIGNAL_ADD, peer);
+}
+
 // "swarm": every thread of the grid does its own get (THREAD_MULTIPLE use of the API).
 __global__ void k_swarm_get(State s, char* local, const char* sym, size_t size, int peer) {
   size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
@@ -221,6 +243,29 @@ int bshmem_gpu_bench_msgrate(bshmem_handle_t h, void* dest_sym, const void* src,
   o->ns = 0; o->status = 0;
   k_put_msgrate<<<ctas, threads, 0, stream>>>(st, static_cast<char*>(dest_sym), static_cast<const char*>(src), size, peer, windows, o);
   return finish(stream, o, ns);
+}
+
+int bshmem_gpu_bench_amo_rate(bshmem_handle_t h, void* target_sym, int words, int peer, int iters, int ctas, int threads, uint64_t* ns) {
+  State st; cudaStream_t stream;
+  int rc = get_state(h, &st, &stream);
+  if (rc != BSHMEM_OK) return rc;
+  if (words < 1 || ctas < 1 || threads < 1 || threads > 1024) return BSHMEM_ERR_INVALID;
+  BenchOut* o = pinned_out();
+  o->ns = 0; o->status = 0;
+  k_amo_rate<<<ctas, threads, 0, stream>>>(st, static_cast<unsigned long long*>(target_sym), words, peer, iters, o);
+  return finish(stream, o, ns);
+}
+
+// Enqueues the one-way put-with-signal stream (time it with CUDA events around the call).
+int bshmem_gpu_put_signal_stream(bshmem_handle_t h, void* data_sym, const void* src, void* sig_sym, uint64_t nbytes, int peer,
+                                 int iters, int ctas, int threads) {
+  State st; cudaStream_t stream;
+  int rc = get_state(h, &st, &stream);
+  if (rc != BSHMEM_OK) return rc;
+  if (ctas < 1 || threads < 32 || threads > 1024) return BSHMEM_ERR_INVALID;
+  k_put_signal_stream<<<ctas, threads, 0, stream>>>(st, static_cast<char*>(data_sym), static_cast<const char*>(src),
+                                                    static_cast<uint64_t*>(sig_sym), nbytes, peer, iters);
+  return cudaGetLastError() == cudaSuccess ? BSHMEM_OK : BSHMEM_ERR_CUDA;
 }
 
 int bshmem_gpu_swarm_get(bshmem_handle_t h, void* local, const void* sym, uint64_t size, int peer, int ctas, int threads) {

@@ -76,6 +76,14 @@ class Backend {
                   uint64_t* fetched) = 0;
   virtual int fence() = 0;
   virtual int quiet() = 0;
+  // Host contexts as ordering domains (one MPI window each in the reference, library/src/host/host.cpp:85-131): a
+  // backend may keep resources per context — the NVLink backend a CUDA stream and pinned result slots, so that
+  // quiet() on a context completes that context's operations only.  ctx_select names the context the calling
+  // thread's next RMA / atomic / fence / quiet belongs to (thread-local; the runtime resets it to the default
+  // context after each call); backends without per-context state ignore all three.
+  virtual int ctx_open(int idx, long options) { (void)idx; (void)options; return BSHMEM_OK; }
+  virtual void ctx_close(int idx) { (void)idx; }
+  virtual void ctx_select(int idx) { (void)idx; }
   // cmp on local symmetric memory; blocks at most timeout_us.
   virtual int wait_until(uint64_t off, int dtype, int cmp, uint64_t value, uint64_t timeout_us) = 0;
   virtual int test(uint64_t off, int dtype, int cmp, uint64_t value, int* result) = 0;

@@ -7,6 +7,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
 #include "runtime.h"
 
@@ -73,8 +74,8 @@ int RuntimeExecutor::execute(const bshmem_proxy_desc_t& d, uint64_t* result) {
 }
 
 uint64_t proxy_ring_bytes(uint64_t capacity) {
-  // slots | completion | result | read_index (own cache line)
-  return capacity * sizeof(bshmem_proxy_desc_t) + capacity * 8 * 2 + 128;
+  // slots | completion | result | consumed | read_index (own cache line)
+  return capacity * sizeof(bshmem_proxy_desc_t) + capacity * 8 * 3 + 128;
 }
 
 bshmem_proxy* proxy_start(void* block, uint64_t capacity, unsigned long long* write_index, unsigned long long timeout_ns,
@@ -89,6 +90,8 @@ bshmem_proxy* proxy_start(void* block, uint64_t capacity, unsigned long long* wr
   px->ring.completion = reinterpret_cast<volatile uint64_t*>(p);
   p += capacity * 8;
   px->ring.result = reinterpret_cast<volatile uint64_t*>(p);
+  p += capacity * 8;
+  px->ring.consumed = reinterpret_cast<volatile uint64_t*>(p);
   p += capacity * 8;
   px->ring.read_index = reinterpret_cast<volatile uint64_t*>(p);
   px->ring.write_index = write_index ? write_index : reinterpret_cast<unsigned long long*>(&px->host_write_index);
@@ -107,6 +110,7 @@ void bshmem_proxy::run() {
   uint64_t read = 0;
   const uint64_t mask = ring.capacity - 1;
   unsigned idle = 0;
+  std::vector<uint8_t> lap_blocking(ring.capacity, 0);
   while (!stop.load(std::memory_order_acquire)) {
     if (paused.load(std::memory_order_acquire)) {
       timespec ts{0, 50000};
@@ -123,6 +127,17 @@ void bshmem_proxy::run() {
     idle = 0;
     bshmem_proxy_desc_t cmd;
     memcpy(&cmd, slot, sizeof(cmd));
+    // The blocking producer that owned this slot one lap ago must have read its result before it is overwritten
+    // (bounded: a producer whose own wait ran out never acknowledges).
+    if (read >= ring.capacity && lap_blocking[read & mask]) {
+      const uint64_t want = read - ring.capacity + 1;
+      const uint64_t deadline = now_ns() + ring.timeout_ns;
+      for (unsigned spins = 0; __atomic_load_n(&ring.consumed[read & mask], __ATOMIC_ACQUIRE) < want; ++spins) {
+        if ((spins & 255) == 255 && now_ns() > deadline) break;
+        backoff(spins);
+      }
+    }
+    lap_blocking[read & mask] = (cmd.flags & BSHMEM_PROXY_FLAG_BLOCKING) != 0;
     int to_drop = drop.load(std::memory_order_acquire);
     if (to_drop > 0 && drop.compare_exchange_strong(to_drop, to_drop - 1)) {
       // injected fault: the command vanishes (neither executed nor completed)
@@ -172,10 +187,17 @@ int bshmem_proxy_host_submit(bshmem_proxy_t* px, const bshmem_proxy_desc_t* cmd,
   if (!px || !cmd) return BSHMEM_ERR_INVALID;
   bshmem_proxy_ring_t& r = px->ring;
   const uint64_t mask = r.capacity - 1;
-  uint64_t ticket = __atomic_fetch_add(r.write_index, 1ull, __ATOMIC_ACQ_REL);
   uint64_t deadline = now_ns() + r.timeout_ns;
-  // back-pressure: the slot is free once the consumer moved past ticket - capacity
-  for (unsigned spins = 0; ticket - __atomic_load_n(r.read_index, __ATOMIC_ACQUIRE) >= r.capacity; ++spins) {
+  // A ticket is only taken while the ring has room for it (the consumer moved past ticket - capacity): a producer
+  // that gives up on a full ring has reserved nothing, so the consumer never waits for a slot nobody will fill.
+  uint64_t ticket;
+  for (unsigned spins = 0;; ++spins) {
+    ticket = __atomic_load_n(r.write_index, __ATOMIC_ACQUIRE);
+    if (ticket - __atomic_load_n(r.read_index, __ATOMIC_ACQUIRE) < r.capacity) {
+      unsigned long long expect = ticket;
+      if (__atomic_compare_exchange_n(r.write_index, &expect, ticket + 1, false, __ATOMIC_ACQ_REL, __ATOMIC_ACQUIRE)) break;
+      continue;
+    }
     if ((spins & 255) == 255 && now_ns() > deadline) return BSHMEM_ERR_TIMEOUT;
     backoff(spins);
   }
@@ -189,6 +211,7 @@ int bshmem_proxy_host_submit(bshmem_proxy_t* px, const bshmem_proxy_desc_t* cmd,
     backoff(spins);
   }
   uint64_t res = r.result[ticket & mask];
+  __atomic_store_n(&r.consumed[ticket & mask], ticket + 1, __ATOMIC_RELEASE);   // the slot's result may be overwritten now
   bool fetches = cmd->op == BSHMEM_PROXY_G || cmd->op == BSHMEM_PROXY_AMO;
   if (fetches) {
     if (result) *result = res;

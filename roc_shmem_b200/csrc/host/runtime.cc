@@ -273,6 +273,15 @@ int bshmem_addr_accessible(bshmem_handle_t h, const void* addr, int pe) {
 }
 
 /* ---- contexts -------------------------------------------------------------- */
+namespace {
+// The backend operations issued inside this scope belong to host context `c`.
+struct CtxScope {
+  Backend* be;
+  CtxScope(bshmem_handle_t h, int c) : be(h->backend.get()) { be->ctx_select(c); }
+  ~CtxScope() { be->ctx_select(0); }
+};
+}  // namespace
+
 int bshmem_team_create_ctx(bshmem_handle_t h, bshmem_team_t team, long options, bshmem_ctx_t* out) {
   CHECK_H(h);
   if (!out) return BSHMEM_ERR_INVALID;
@@ -282,6 +291,8 @@ int bshmem_team_create_ctx(bshmem_handle_t h, bshmem_team_t team, long options, 
   std::lock_guard<std::mutex> g(h->mu);
   for (size_t i = 1; i < h->ctxs.size(); ++i) {
     if (!h->ctxs[i] || !h->ctxs[i]->live) {
+      int rc = h->backend->ctx_open((int)i, options);
+      if (rc != BSHMEM_OK) return h->fail(rc, "ctx_create: the backend could not open the context");
       h->ctxs[i].reset(new HostContext());
       h->ctxs[i]->live = true;
       h->ctxs[i]->options = options;
@@ -304,7 +315,11 @@ int bshmem_ctx_destroy(bshmem_handle_t h, bshmem_ctx_t c) {
   if (c == BSHMEM_CTX_DEFAULT) return BSHMEM_OK;   // the default context lives until finalize
   HostContext* x = h->ctx(c);
   if (!x) return BSHMEM_ERR_INVALID;
-  h->backend->quiet();   // destroying a context completes its operations
+  {
+    CtxScope sel(h, c);
+    h->backend->quiet();   // destroying a context completes its operations
+  }
+  h->backend->ctx_close(c);
   std::lock_guard<std::mutex> g(h->mu);
   x->live = false;
   h->global_stats.inc(ST_CTX_DESTROY);
@@ -372,6 +387,7 @@ int bshmem_team_translate_pe(bshmem_handle_t h, bshmem_team_t src, int src_pe, b
 }
 
 /* ---- RMA ------------------------------------------------------------------- */
+
 static int do_put(bshmem_handle_t h, int c, void* dest, const void* src, size_t n, int pe, bool nbi) {
   CHECK_H(h);
   HostContext* x = h->ctx(c);
@@ -384,6 +400,7 @@ static int do_put(bshmem_handle_t h, int c, void* dest, const void* src, size_t 
   if (!h->to_offset(dest, n, &off)) return h->fail(BSHMEM_ERR_RANGE, "put: dest is not symmetric");
   STAT(h, x, nbi ? ST_PUT_NBI : ST_PUT);
   STAT(h, x, ST_BYTES_PUT, n);
+  CtxScope sel(h, c);
   return h->backend->put(wpe, off, src, n, nbi);
 }
 
@@ -399,6 +416,7 @@ static int do_get(bshmem_handle_t h, int c, void* dest, const void* src, size_t 
   if (!h->to_offset(src, n, &off)) return h->fail(BSHMEM_ERR_RANGE, "get: source is not symmetric");
   STAT(h, x, nbi ? ST_GET_NBI : ST_GET);
   STAT(h, x, ST_BYTES_GET, n);
+  CtxScope sel(h, c);
   return h->backend->get(wpe, dest, off, n, nbi);
 }
 
@@ -420,6 +438,7 @@ static int do_put_signal(bshmem_handle_t h, int c, void* dest, const void* src, 
   if (!h->to_offset(sig, 8, &soff) || (soff & 7)) return h->fail(BSHMEM_ERR_RANGE, "put_signal: signal word is not symmetric / aligned");
   STAT(h, x, ST_PUT_SIGNAL);
   STAT(h, x, ST_BYTES_PUT, n);
+  CtxScope sel(h, c);
   return h->backend->put_signal(wpe, off, src, n, soff, val, sig_op, nbi);
 }
 
@@ -450,6 +469,7 @@ int bshmem_ctx_amo(bshmem_handle_t h, bshmem_ctx_t c, int dtype, int op, void* d
   if (!h->to_offset(dest, sz, &off) || (off & (sz - 1))) return h->fail(BSHMEM_ERR_RANGE, "amo: dest is not symmetric / aligned");
   STAT(h, x, kAmoStat[op]);
   uint64_t tmp = 0;
+  CtxScope sel(h, c);
   int rc = h->backend->amo(wpe, off, dtype, op, value, cond, &tmp);
   if (fetched) *fetched = tmp;
   return rc;
@@ -461,6 +481,7 @@ int bshmem_ctx_fence(bshmem_handle_t h, bshmem_ctx_t c) {
   HostContext* x = h->ctx(c);
   if (!x) return BSHMEM_ERR_INVALID;
   STAT(h, x, ST_FENCE);
+  CtxScope sel(h, c);
   return h->backend->fence();
 }
 
@@ -469,6 +490,7 @@ int bshmem_ctx_quiet(bshmem_handle_t h, bshmem_ctx_t c) {
   HostContext* x = h->ctx(c);
   if (!x) return BSHMEM_ERR_INVALID;
   STAT(h, x, ST_QUIET);
+  CtxScope sel(h, c);
   return h->backend->quiet();
 }
 

@@ -82,8 +82,37 @@ __device__ __forceinline__ int active_set_sync(const State& s, const Team& t) {
 // sync: every member's channel `cta` has arrived.  Does not complete RMA by itself,
 // but publishes the calling block's earlier stores (fence before the flag stores).
 // Returns BSHMEM_OK or BSHMEM_ERR_TIMEOUT (same value in every thread of the block).
+// World team with an NVLink multicast mapping: every PE adds 1 to channel `cta`'s counter in ALL heaps with one
+// multimem.red (the switch replicates it) and waits until its own copy has counted every member of this epoch.
+// One store per PE instead of size-1 flag stores; counters are monotonic.
+__device__ __forceinline__ int team_sync_mc(const State& s, const Team& t, int cta) {
+  __shared__ int mc_status;
+  unsigned long long t0 = s.stats ? dev::timer() : 0;
+  __syncthreads();                       // all stores of the block precede the release below
+  if (threadIdx.x == 0) {
+    unsigned long long* ep = reinterpret_cast<unsigned long long*>(s.heap_base[s.my_pe] + BSHMEM_OFF_MCBAR) + BSHMEM_MAX_COLL_CTAS + cta;
+    const unsigned long long epoch = *ep + 1;
+    const uint64_t off = BSHMEM_OFF_MCBAR + (uint64_t)cta * 8;
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(s.mc_base + off), "l"(1ull) : "memory");
+    mc_status = dev::wait_until<uint64_t>(s, reinterpret_cast<const uint64_t*>(s.heap_base[s.my_pe] + off), BSHMEM_CMP_GE,
+                                          epoch * (uint64_t)t.size, BSHMEM_WHERE_BARRIER, -1);
+    *ep = epoch;
+    if (s.stats) {
+      dev::stat(s, BSHMEM_DSTAT_BARRIER);
+      dev::stat(s, BSHMEM_DSTAT_BARRIER_NS, dev::timer() - t0);
+      dev::trace(s, BSHMEM_TRACE_BARRIER, s.my_pe, dev::timer() - t0);
+    }
+  }
+  __syncthreads();
+  int rc = mc_status;
+  __syncthreads();
+  return rc;
+}
+
 __device__ __forceinline__ int team_sync(const State& s, const Team& t, int cta = 0) {
   if (t.slot < 0) return active_set_sync(s, t);
+  if (t.slot == 0 && t.size == s.n_pes && s.mc_base != nullptr && s.n_pes > 1) return team_sync_mc(s, t, cta);
   __shared__ int sync_status;
   const int tid = threadIdx.x;
   unsigned long long t0 = s.stats ? dev::timer() : 0;
@@ -210,17 +239,18 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
   using A = typename Acc<T>::type;
   constexpr int VE = 16 / sizeof(T);
   const int tid = threadIdx.x, nth = blockDim.x;
-  // all sources and destinations share the symmetric offset, so one alignment check covers them
   size_t vbeg = (begin + VE - 1) / VE * VE, vend = end / VE * VE;
-  bool aligned = ((uintptr_t)srcs[0] & 15) == 0 && ((uintptr_t)dsts[0] & 15) == 0;
+  // sources are usually the same symmetric offset on every member, but staged collectives mix a staging block per
+  // sender with the local source, so every pointer is checked
+  bool aligned = true;
+  for (int k = 0; k < nsrc; ++k) aligned &= ((uintptr_t)srcs[k] & 15) == 0;
+  for (int d = 0; d < ndst; ++d) aligned &= ((uintptr_t)dsts[d] & 15) == 0;
   if (!aligned || vbeg >= vend) { vbeg = vend = begin; }
   for (size_t i = begin + tid; i < vbeg; i += nth) {
     A acc = to_acc<T>(srcs[0][i]);
     for (int k = 1; k < nsrc; ++k) acc = apply<A>(op, acc, to_acc<T>(srcs[k][i]));
     for (int d = 0; d < ndst; ++d) dsts[d][i] = from_acc<T>(acc);
   }
-  // vector body: enough independent 16-byte loads per thread (members x unroll ~ 16) to cover the NVLink
-  // latency whatever the team size
   const size_t v0 = vbeg / VE, v1 = vend / VE;
   // the unrolled variants exist for the element types and operators of bulk reductions (sum / max / min of
   // float, double, half, bf16, int32, int64); everything else takes the generic body, which keeps the build short
@@ -228,6 +258,8 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
                         (std::is_same<T, float>::value || std::is_same<T, double>::value || std::is_same<T, __half>::value ||
                          std::is_same<T, __nv_bfloat16>::value || std::is_same<T, int32_t>::value || std::is_same<T, long long>::value);
   if constexpr (kHot) {
+    // members x unroll = 16 independent 16-byte loads per thread (64 registers; the reduction kernels run 256-thread
+    // blocks, so nothing spills): with ~100 blocks several megabytes are in flight, which NVLink's latency needs
     if (nsrc <= 2) reduce_vec_body<T, OP, 2, 8>(nsrc, srcs, ndst, dsts, v0, v1);
     else if (nsrc <= 4) reduce_vec_body<T, OP, 4, 4>(nsrc, srcs, ndst, dsts, v0, v1);
     else if (nsrc <= 8) reduce_vec_body<T, OP, 8, 2>(nsrc, srcs, ndst, dsts, v0, v1);
@@ -274,9 +306,11 @@ __device__ __forceinline__ void split_range(size_t n, int parts, int idx, size_t
 
 constexpr size_t kOneShotBytes = 64 * 1024;   // below this every PE reduces the whole vector itself
 
-static_assert(BSHMEM_OFF_SCRATCH + BSHMEM_SCRATCH_BYTES <= BSHMEM_OFF_LL && BSHMEM_OFF_LL + BSHMEM_LL_BYTES <= BSHMEM_OFF_SLAB &&
+static_assert(BSHMEM_OFF_SCRATCH + BSHMEM_SCRATCH_BYTES <= BSHMEM_OFF_MCBAR && BSHMEM_OFF_MCBAR + BSHMEM_MCBAR_BYTES <= BSHMEM_OFF_LL &&
+              BSHMEM_OFF_LLT + (uint64_t)BSHMEM_MAX_TEAMS * BSHMEM_LLT_TEAM_BYTES <= BSHMEM_OFF_STAGE &&
+              BSHMEM_OFF_STAGE + 2 * BSHMEM_STAGE_BYTES <= BSHMEM_INTERNAL_BYTES && BSHMEM_OFF_LL + BSHMEM_LL_BYTES <= BSHMEM_OFF_SLAB &&
               BSHMEM_OFF_SLAB + BSHMEM_SLAB_BYTES <= BSHMEM_OFF_LLB && BSHMEM_OFF_LLB + BSHMEM_LLB_BYTES <= BSHMEM_OFF_LLT &&
-              BSHMEM_OFF_LLT + (uint64_t)BSHMEM_MAX_TEAMS * BSHMEM_LLT_TEAM_BYTES <= BSHMEM_INTERNAL_BYTES,
+              BSHMEM_OFF_SCRATCH + BSHMEM_SCRATCH_BYTES <= BSHMEM_OFF_LL,
               "internal heap regions overlap");
 
 // Low-latency allreduce for small vectors on the world team, single block: ONE NVLink exchange instead of
@@ -472,6 +506,136 @@ __device__ __forceinline__ int team_alltoall(const State& s, const Team& t, void
   return team_barrier(s, t, cta);
 }
 
+
+// ---- one-exchange collectives through the staging region (world team, host-launched) -------------------------
+// The sync + work + barrier forms above pay two flag exchanges because a PE may only write into a peer's `dest`
+// once that peer has entered the call.  Here every PE pushes into a runtime-owned per-sender block on the peer
+// instead (always writable: see the parity argument), then ONE barrier tells everybody that all blocks have landed,
+// and each PE copies / reduces its staging into `dest` locally.  `seq` is a call sequence number the host supplies,
+// the same on every PE; consecutive calls alternate between the two staging halves.  A PE writes half (seq & 1)
+// again two staged calls later; it has then completed call seq+1, whose barrier needed every peer's kernel of call
+// seq+1 to be running, and kernels of one PE run in stream order, so every peer has finished reading call seq's half.
+__device__ __forceinline__ char* stage_half(const State& s, int pe, unsigned long long seq) {
+  return s.heap_base[pe] + BSHMEM_OFF_STAGE + (seq & 1) * BSHMEM_STAGE_BYTES;
+}
+// 16-byte-vector copy of the block's range into the same offset of EVERY PE's heap through the multicast mapping
+__device__ __forceinline__ void copy_bytes_mc(char* mc_dst, const char* src, size_t n) {
+  const uint4* s4 = reinterpret_cast<const uint4*>(src);
+  for (size_t v = threadIdx.x; v < (n >> 4); v += blockDim.x) {
+    const uint4 x = s4[v];
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_dst + v * 16), "r"(x.x), "r"(x.y), "r"(x.z), "r"(x.w) : "memory");
+  }
+}
+
+__device__ __forceinline__ int team_fcollect_staged(const State& s, const Team& t, void* dest, const void* source, size_t nbytes,
+                                                    unsigned long long seq, int use_mc, int cta, int ncta) {
+  size_t b, e;
+  split_range(nbytes, ncta, cta, 16, &b, &e);
+  const char* src = reinterpret_cast<const char*>(source);
+  const size_t mine = (size_t)t.my_idx * nbytes;
+  if (use_mc && s.mc_base) {
+    // one multicast store per vector lands in block my_idx of every PE's staging half (this PE's included)
+    copy_bytes_mc(s.mc_base + BSHMEM_OFF_STAGE + (seq & 1) * BSHMEM_STAGE_BYTES + mine + b, src + b, e - b);
+  } else {
+    for (int k = 1; k < t.size; ++k) {
+      const int idx = (t.my_idx + k) % t.size;
+      dev::copy_bytes<dev::BLOCK>(stage_half(s, dev::team_pe(t, idx), seq) + mine + b, src + b, e - b);
+    }
+  }
+  dev::copy_bytes<dev::BLOCK>(reinterpret_cast<char*>(dest) + mine + b, src + b, e - b);
+  int rc = team_barrier(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  const char* st = stage_half(s, s.my_pe, seq);
+  for (int k = 1; k < t.size; ++k) {
+    const size_t o = (size_t)((t.my_idx + k) % t.size) * nbytes + b;
+    dev::copy_bytes<dev::BLOCK>(reinterpret_cast<char*>(dest) + o, st + o, e - b);
+  }
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, nbytes); }
+  return BSHMEM_OK;
+}
+
+__device__ __forceinline__ int team_alltoall_staged(const State& s, const Team& t, void* dest, const void* source, size_t nbytes,
+                                                    unsigned long long seq, int cta, int ncta) {
+  size_t b, e;
+  split_range(nbytes, ncta, cta, 16, &b, &e);
+  const char* src = reinterpret_cast<const char*>(source);
+  const size_t mine = (size_t)t.my_idx * nbytes;
+  for (int k = 1; k < t.size; ++k) {
+    const int j = (t.my_idx + k) % t.size;
+    dev::copy_bytes<dev::BLOCK>(stage_half(s, dev::team_pe(t, j), seq) + mine + b, src + (size_t)j * nbytes + b, e - b);
+  }
+  dev::copy_bytes<dev::BLOCK>(reinterpret_cast<char*>(dest) + mine + b, src + mine + b, e - b);
+  int rc = team_barrier(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  const char* st = stage_half(s, s.my_pe, seq);
+  for (int k = 1; k < t.size; ++k) {
+    const size_t o = (size_t)((t.my_idx + k) % t.size) * nbytes + b;
+    dev::copy_bytes<dev::BLOCK>(reinterpret_cast<char*>(dest) + o, st + o, e - b);
+  }
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, nbytes); }
+  return BSHMEM_OK;
+}
+
+// reduce-scatter: every PE pushes slice j of its source into PE j's staging, one barrier, local reduction (own slice
+// straight from `source`).  n elements per PE; n * sizeof(T) is a multiple of 16 and source is 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ int team_reduce_scatter_staged(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
+                                                          unsigned long long seq, int cta, int ncta) {
+  size_t b, e;
+  split_range(n, ncta, cta, 16 / sizeof(T), &b, &e);
+  const size_t slot = n * sizeof(T);
+  for (int k = 1; k < t.size; ++k) {
+    const int j = (t.my_idx + k) % t.size;
+    dev::copy_bytes<dev::BLOCK>(stage_half(s, dev::team_pe(t, j), seq) + (size_t)t.my_idx * slot + b * sizeof(T),
+                                reinterpret_cast<const char*>(source + (size_t)j * n + b), (e - b) * sizeof(T));
+  }
+  int rc = team_barrier(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  const T* srcs[BSHMEM_MAX_PES];
+  const char* st = stage_half(s, s.my_pe, seq);
+  for (int k = 0; k < t.size; ++k)
+    srcs[k] = k == t.my_idx ? source + (size_t)t.my_idx * n : reinterpret_cast<const T*>(st + (size_t)k * slot);
+  T* mine[1] = {dest};
+  reduce_range<T>(op, t.size, srcs, 1, mine, b, e);
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, slot); }
+  return BSHMEM_OK;
+}
+
+// allreduce, two exchanges: staged reduce-scatter of uneven 16-byte-granular slices, then every PE writes its reduced
+// slice into every member's dest (safe: after the first barrier all members are in this call and have finished
+// reading their sources, so dest may even alias source) and a closing barrier delivers the results.
+template <typename T>
+__device__ __forceinline__ int team_reduce_staged(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
+                                                  unsigned long long seq, int cta, int ncta) {
+  constexpr size_t VE = 16 / sizeof(T);
+  const size_t slot = (BSHMEM_STAGE_BYTES / t.size) & ~(size_t)15;   // room per sender; a slice is at most ceil(n / size) elements
+  for (int k = 1; k < t.size; ++k) {
+    const int j = (t.my_idx + k) % t.size;
+    size_t sb, se, b, e;
+    split_range(n, t.size, j, VE, &sb, &se);
+    split_range(se - sb, ncta, cta, VE, &b, &e);
+    dev::copy_bytes<dev::BLOCK>(stage_half(s, dev::team_pe(t, j), seq) + (size_t)t.my_idx * slot + b * sizeof(T),
+                                reinterpret_cast<const char*>(source + sb + b), (e - b) * sizeof(T));
+  }
+  int rc = team_barrier(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  size_t sb, se, b, e;
+  split_range(n, t.size, t.my_idx, VE, &sb, &se);
+  split_range(se - sb, ncta, cta, VE, &b, &e);
+  const T* srcs[BSHMEM_MAX_PES];
+  T* dsts[BSHMEM_MAX_PES];
+  const char* st = stage_half(s, s.my_pe, seq);
+  for (int k = 0; k < t.size; ++k) {
+    // index i of reduce_range runs over [sb + b, sb + e): staged blocks start at element 0 of the slice
+    srcs[k] = k == t.my_idx ? source : reinterpret_cast<const T*>(st + (size_t)k * slot) - sb;
+    dsts[k] = dev::ptr(s, dest, dev::team_pe(t, k));
+  }
+  reduce_range<T>(op, t.size, srcs, t.size, dsts, sb + b, sb + e);
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, n * sizeof(T)); }
+  return team_barrier(s, t, cta);
+}
+
 // ---- NVLink-multicast (NVLS) allreduce: the switch reduces and broadcasts ----------------------
 // Works on 16-byte vectors of fp32 / bf16 sum only; the caller falls back otherwise.
 template <typename T>
@@ -529,6 +693,24 @@ template <typename T> __device__ __forceinline__ int wg_fcollect(const State& s,
 }
 template <typename T> __device__ __forceinline__ int wg_alltoall(const State& s, const Team& t, T* dest, const T* src, size_t n) {
   return team_alltoall(s, t, dest, src, n * sizeof(T), 0, 1);
+}
+
+
+// context forms (library/include/roc_shmem.hpp:754-795, 838-1160): the context's team is the team of the collective
+__device__ __forceinline__ int ctx_wg_barrier_all(const State& s, const dev::Ctx&) { return wg_barrier_all(s); }
+__device__ __forceinline__ int ctx_wg_sync_all(const State& s, const dev::Ctx&) { return wg_sync_all(s); }
+__device__ __forceinline__ int ctx_wg_team_sync(const State& s, const dev::Ctx& c) { return team_sync(s, c.team); }
+template <typename T> __device__ __forceinline__ int ctx_wg_to_all(const State& s, const dev::Ctx& c, int op, T* dest, const T* src, size_t n) {
+  return wg_to_all<T>(s, c.team, op, dest, src, n);
+}
+template <typename T> __device__ __forceinline__ int ctx_wg_broadcast(const State& s, const dev::Ctx& c, T* dest, const T* src, size_t n, int root) {
+  return wg_broadcast<T>(s, c.team, dest, src, n, root);
+}
+template <typename T> __device__ __forceinline__ int ctx_wg_fcollect(const State& s, const dev::Ctx& c, T* dest, const T* src, size_t n) {
+  return wg_fcollect<T>(s, c.team, dest, src, n);
+}
+template <typename T> __device__ __forceinline__ int ctx_wg_alltoall(const State& s, const dev::Ctx& c, T* dest, const T* src, size_t n) {
+  return wg_alltoall<T>(s, c.team, dest, src, n);
 }
 
 }  // namespace coll

@@ -26,7 +26,16 @@
 #include "bshmem_types.h"
 
 // ---- layout of the runtime-internal region at the start of every heap ----------
-#define BSHMEM_INTERNAL_BYTES (40ull << 20)
+#define BSHMEM_INTERNAL_BYTES (72ull << 20)
+/* Staging for one-exchange collectives of the world team (host-launched; fcollect, alltoall, reduce-scatter and the
+ * first half of mid-size allreduces): 40 MiB .. 72 MiB, [2 parities][16 MiB]; sender k's block starts at k * (bytes
+ * per sender).  The parity is the low bit of a call sequence number that the host supplies (same on every PE).     */
+#define BSHMEM_OFF_STAGE (40ull << 20)
+#define BSHMEM_STAGE_BYTES (16ull << 20)
+/* Multicast barrier of the world team: per channel, a counter every PE adds to with one multimem.red (replicated in
+ * every heap) and a local epoch word.                                                                            */
+#define BSHMEM_OFF_MCBAR (960ull << 10)
+#define BSHMEM_MCBAR_BYTES (2ull * BSHMEM_MAX_COLL_CTAS * 8)
 /* Low-latency allreduce slots for host-launched, multi-block calls (epoch supplied by the host): 4 MiB .. 36 MiB,
  * [2 parities][sender PE][512 KiB of payload as 8-byte words].                                                    */
 #define BSHMEM_OFF_LLB (4ull << 20)
@@ -232,6 +241,70 @@ __device__ __forceinline__ void copy_bytes(char* __restrict__ dst, const char* _
   } else {
     for (size_t i = r; i < n; i += w) dst[i] = src[i];
   }
+}
+
+// ---- large-message copy engine: bulk async copies staged through shared memory --------------------------
+// One thread drives a ring of kStages chunks: cp.async.bulk global -> shared (completion on an mbarrier), then
+// cp.async.bulk shared -> global (bulk-group completion).  Either side may be a peer's memory; nothing here is a
+// multicast copy.  No registers carry payload, so one CTA keeps (kStages - 1) * kChunk bytes of loads in flight.
+// Needs 16-byte aligned src, dst and n, `smem` of kStages * kChunk bytes (16-byte aligned) plus kStages mbarriers.
+// Block scope: every thread calls; returns BSHMEM_OK or BSHMEM_ERR_TIMEOUT (a bounded mbarrier wait ran out).
+template <int kStages, int kChunk>
+__device__ __forceinline__ int bulk_copy_block(const State& s, char* dst, const char* src, size_t n, char* smem, uint64_t* bars) {
+  __shared__ int bulk_status;
+  if (threadIdx.x == 0) {
+    bulk_status = BSHMEM_OK;
+    for (int i = 0; i < kStages; ++i)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&bars[i])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const size_t nchunks = (n + kChunk - 1) / kChunk;
+    auto issue_load = [&](size_t k) {
+      const int st = (int)(k % kStages);
+      const uint32_t bytes = (uint32_t)((k + 1) * (size_t)kChunk <= n ? kChunk : n - k * (size_t)kChunk);
+      const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&bars[st]);
+      const uint32_t sm = (uint32_t)__cvta_generic_to_shared(smem + (size_t)st * kChunk);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(sm), "l"(src + k * (size_t)kChunk), "r"(bytes), "r"(bar) : "memory");
+    };
+    for (size_t k = 0; k < nchunks && k < (size_t)(kStages - 1); ++k) issue_load(k);
+    const unsigned long long t0 = timer();
+    for (size_t i = 0; i < nchunks; ++i) {
+      const int st = (int)(i % kStages);
+      const uint32_t parity = (uint32_t)((i / kStages) & 1);
+      const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&bars[st]);
+      uint32_t ok = 0, it = 0;
+      while (true) {
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) break;
+        if ((++it & 63) == 0 && timer() - t0 > s.timeout_ns) {
+          record_error(s, BSHMEM_ERR_TIMEOUT, -1, BSHMEM_WHERE_MBARRIER, (uint64_t)(src + i * (size_t)kChunk), i, 0);
+          bulk_status = BSHMEM_ERR_TIMEOUT;
+          break;
+        }
+      }
+      if (!ok) break;
+      const uint32_t bytes = (uint32_t)((i + 1) * (size_t)kChunk <= n ? kChunk : n - i * (size_t)kChunk);
+      const uint32_t sm = (uint32_t)__cvta_generic_to_shared(smem + (size_t)st * kChunk);
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + i * (size_t)kChunk), "r"(sm), "r"(bytes) : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      // chunk i + kStages - 1 goes into the stage chunk i - 1 was stored from: that store must have read its data
+      const size_t nxt = i + kStages - 1;
+      if (nxt < nchunks) {
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        issue_load(nxt);
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // every store has been written
+  }
+  __syncthreads();
+  const int rc = bulk_status;
+  __syncthreads();
+  return rc;
 }
 
 // ---- RMA ------------------------------------------------------------------------------------
@@ -455,14 +528,86 @@ __device__ __forceinline__ int wg_team_create_ctx(const State&, const Team& team
   return BSHMEM_OK;
 }
 __device__ __forceinline__ void wg_ctx_destroy(Ctx*) {}
+// ---- context forms of every operation ------------------------------------------------------------------
+// PE arguments are relative to the context's team (world numbering for a context made by wg_ctx_create), for
+// RMA, atomics, put-with-signal and fence(pe) alike; BSHMEM_CTX_NOSTORE skips the fence that publishes the
+// caller's earlier plain stores after a blocking put.  Parity: library/include/roc_shmem.hpp:559-725 (ctx RMA,
+// fence, quiet, p/g), :1548-1953 (ctx AMOs), library/src/roc_shmem_gpu.cpp:240-247 (translate_pe), :298-661.
 __device__ __forceinline__ int ctx_pe(const Ctx& c, int pe) { return team_pe(c.team, pe); }
+__device__ __forceinline__ int ctx_my_pe(const Ctx& c) { return c.team.my_idx; }
+__device__ __forceinline__ int ctx_n_pes(const Ctx& c) { return c.team.size; }
+__device__ __forceinline__ void ctx_fence(const State& s, const Ctx&) { fence(s); }
+__device__ __forceinline__ void ctx_fence(const State& s, const Ctx& c, int pe) { fence_pe(s, ctx_pe(c, pe)); }
+__device__ __forceinline__ void ctx_quiet(const State& s, const Ctx&) { quiet(s); }
+template <typename T> __device__ __forceinline__ T* ctx_ptr(const State& s, const Ctx& c, const T* local, int pe) { return ptr(s, local, ctx_pe(c, pe)); }
+
 template <Scope S = THREAD>
 __device__ __forceinline__ void ctx_putmem(const State& s, const Ctx& c, void* dest, const void* src, size_t n, int pe) {
   putmem<S>(s, dest, src, n, ctx_pe(c, pe), c.options);
 }
 template <Scope S = THREAD>
+__device__ __forceinline__ void ctx_putmem_nbi(const State& s, const Ctx& c, void* dest, const void* src, size_t n, int pe) {
+  putmem_nbi<S>(s, dest, src, n, ctx_pe(c, pe));
+}
+template <Scope S = THREAD>
 __device__ __forceinline__ void ctx_getmem(const State& s, const Ctx& c, void* dest, const void* src, size_t n, int pe) {
   getmem<S>(s, dest, src, n, ctx_pe(c, pe));
+}
+template <Scope S = THREAD>
+__device__ __forceinline__ void ctx_getmem_nbi(const State& s, const Ctx& c, void* dest, const void* src, size_t n, int pe) {
+  getmem_nbi<S>(s, dest, src, n, ctx_pe(c, pe));
+}
+template <typename T, Scope S = THREAD>
+__device__ __forceinline__ void ctx_put(const State& s, const Ctx& c, T* dest, const T* src, size_t nelems, int pe) {
+  putmem<S>(s, dest, src, nelems * sizeof(T), ctx_pe(c, pe), c.options);
+}
+template <typename T, Scope S = THREAD>
+__device__ __forceinline__ void ctx_put_nbi(const State& s, const Ctx& c, T* dest, const T* src, size_t nelems, int pe) {
+  putmem_nbi<S>(s, dest, src, nelems * sizeof(T), ctx_pe(c, pe));
+}
+template <typename T, Scope S = THREAD>
+__device__ __forceinline__ void ctx_get(const State& s, const Ctx& c, T* dest, const T* src, size_t nelems, int pe) {
+  getmem<S>(s, dest, src, nelems * sizeof(T), ctx_pe(c, pe));
+}
+template <typename T, Scope S = THREAD>
+__device__ __forceinline__ void ctx_get_nbi(const State& s, const Ctx& c, T* dest, const T* src, size_t nelems, int pe) {
+  getmem_nbi<S>(s, dest, src, nelems * sizeof(T), ctx_pe(c, pe));
+}
+template <typename T> __device__ __forceinline__ void ctx_p(const State& s, const Ctx& c, T* dest, T value, int pe) { p(s, dest, value, ctx_pe(c, pe)); }
+template <typename T> __device__ __forceinline__ T ctx_g(const State& s, const Ctx& c, const T* src, int pe) { return g(s, src, ctx_pe(c, pe)); }
+template <Scope S = THREAD>
+__device__ __forceinline__ void ctx_putmem_signal(const State& s, const Ctx& c, void* dest, const void* src, size_t n,
+                                                  uint64_t* sig_addr, uint64_t signal, int sig_op, int pe) {
+  putmem_signal<S>(s, dest, src, n, sig_addr, signal, sig_op, ctx_pe(c, pe));
+}
+// the 15 atomics, one line per signature class
+#define BSHMEM_DEV_CTX_AMO_VALUE(RET, NAME)                                                                           \
+  template <typename T> __device__ __forceinline__ RET ctx_##NAME(const State& s, const Ctx& c, T* dest, T value, int pe) { \
+    return NAME(s, dest, value, ctx_pe(c, pe));                                                                         \
+  }
+#define BSHMEM_DEV_CTX_AMO_NOVALUE(RET, NAME)                                                                         \
+  template <typename T> __device__ __forceinline__ RET ctx_##NAME(const State& s, const Ctx& c, T* dest, int pe) {      \
+    return NAME(s, dest, ctx_pe(c, pe));                                                                                \
+  }
+BSHMEM_DEV_CTX_AMO_VALUE(T, atomic_fetch_add)
+BSHMEM_DEV_CTX_AMO_VALUE(void, atomic_add)
+BSHMEM_DEV_CTX_AMO_VALUE(T, atomic_swap)
+BSHMEM_DEV_CTX_AMO_VALUE(void, atomic_set)
+BSHMEM_DEV_CTX_AMO_VALUE(T, atomic_fetch_and)
+BSHMEM_DEV_CTX_AMO_VALUE(void, atomic_and)
+BSHMEM_DEV_CTX_AMO_VALUE(T, atomic_fetch_or)
+BSHMEM_DEV_CTX_AMO_VALUE(void, atomic_or)
+BSHMEM_DEV_CTX_AMO_VALUE(T, atomic_fetch_xor)
+BSHMEM_DEV_CTX_AMO_VALUE(void, atomic_xor)
+BSHMEM_DEV_CTX_AMO_NOVALUE(T, atomic_fetch_inc)
+BSHMEM_DEV_CTX_AMO_NOVALUE(void, atomic_inc)
+#undef BSHMEM_DEV_CTX_AMO_VALUE
+#undef BSHMEM_DEV_CTX_AMO_NOVALUE
+template <typename T> __device__ __forceinline__ T ctx_atomic_fetch(const State& s, const Ctx& c, const T* src, int pe) {
+  return atomic_fetch(s, src, ctx_pe(c, pe));
+}
+template <typename T> __device__ __forceinline__ T ctx_atomic_compare_swap(const State& s, const Ctx& c, T* dest, T cond, T value, int pe) {
+  return atomic_compare_swap(s, dest, cond, value, ctx_pe(c, pe));
 }
 
 }  // namespace dev

@@ -46,6 +46,8 @@ uint64_t bshmem_gpu_heap_bytes(void* heap);
 int bshmem_gpu_init(void* heap, const bshmem_config_t* cfg, int coll_ctas, int own_heap, bshmem_handle_t* out);
 int bshmem_gpu_set_stream(bshmem_handle_t h, void* stream);
 int bshmem_gpu_get_stream(bshmem_handle_t h, void** stream);
+int bshmem_gpu_get_device(bshmem_handle_t h, int* device);
+int bshmem_gpu_bind_thread_ctx(bshmem_handle_t h, int ctx);
 int bshmem_gpu_synchronize(bshmem_handle_t h);
 int bshmem_gpu_set_blocking(bshmem_handle_t h, int blocking);
 /* micro-benchmarks and device-API test kernels (p2p_kernels.cu); times in ns from %globaltimer */
@@ -55,8 +57,13 @@ int bshmem_gpu_bench_put_signal(bshmem_handle_t h, void* data_sym, void* sig_sym
 int bshmem_gpu_bench_amo(bshmem_handle_t h, void* target_sym, int peer, int iters, int op, uint64_t* ns);
 int bshmem_gpu_bench_msgrate(bshmem_handle_t h, void* dest_sym, const void* src, uint64_t size, int peer, int windows,
                              int ctas, int threads, uint64_t* ns);
+int bshmem_gpu_bench_amo_rate(bshmem_handle_t h, void* target_sym, int words, int peer, int iters, int ctas, int threads, uint64_t* ns);
+int bshmem_gpu_put_signal_stream(bshmem_handle_t h, void* data_sym, const void* src, void* sig_sym, uint64_t nbytes, int peer,
+                                 int iters, int ctas, int threads);
 int bshmem_gpu_swarm_get(bshmem_handle_t h, void* local, const void* sym, uint64_t size, int peer, int ctas, int threads);
 int bshmem_gpu_api_selftest(bshmem_handle_t h, void* sym_i, void* sym_u, void* sym_f, int peer, int* results_dev);
+int bshmem_gpu_api_matrix(bshmem_handle_t h, void* ring_dev, int team_slot, void* sym_i, void* sym_u, void* sym_f, void* data_sym,
+                          void* local_dev, void* coll_sym, int nbytes, int peer, int* results_dev);
 int bshmem_gpu_wg_collectives(bshmem_handle_t h, void* dst_sym, void* src_sym, int n, int* status_out);
 int bshmem_gpu_set_coll_ctas(bshmem_handle_t h, int n);
 int bshmem_gpu_set_nvls(bshmem_handle_t h, int on);

@@ -17,8 +17,14 @@
  *     exactly as for bshmem_gpu_group_collective();
  *   - more than 16 PEs is rejected with BSHMEM_ERR_LIMIT and a message available from
  *     bshmem_gpu_noalloc_last_error();
+ *   - the array belongs to the CURRENT device, which therefore has to be the device the
+ *     group's heaps live on (anything else is refused with BSHMEM_ERR_STATE); offsets and
+ *     counts that leave the symmetric heap are refused with BSHMEM_ERR_RANGE, and the
+ *     number of CTAs is capped at BSHMEM_MAX_COLL_CTAS;
  *   - the first call on a device looks the array's device address up (once per device,
  *     with that device current).  Make that first call outside any stream capture;
+ *   - the status word is read back on the PE's own stream, so the call synchronises
+ *     with that stream only;
  *   - every call on a device reuses the same array and it keeps the previous call's
  *     contents, so the entry rewrites the table and clears the status word each time.
  *     Two calls that overlap on the GPU (different streams, or different host threads

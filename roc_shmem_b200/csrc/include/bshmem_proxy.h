@@ -2,11 +2,15 @@
  * producers (bshmem_proxy_device.cuh), the host service thread (host/proxy.cc) and
  * host-side producers used in tests.
  *
- * A producer reserves a slot with a ticket, fills a 128-byte descriptor, publishes
- * it by storing ticket+1 to the descriptor's `valid` word (on its own cache line)
- * and, for blocking operations, waits — bounded — for the same value in the slot's
- * completion word.  The consumer executes descriptors strictly in ticket order and
- * publishes its read index for back-pressure.
+ * A producer reserves a slot with a ticket — only while the ring has room, so a
+ * producer that gives up on a full ring leaves no hole in the ticket sequence —
+ * fills a 128-byte descriptor, publishes it by storing ticket+1 to the descriptor's
+ * `valid` word (on its own cache line) and, for blocking operations, waits — bounded
+ * — for the same value in the slot's completion word, reads the result word and
+ * acknowledges in the slot's `consumed` word.  The consumer executes descriptors
+ * strictly in ticket order, publishes its read index for back-pressure, and does not
+ * overwrite a slot's result before the blocking producer that owned the slot one lap
+ * earlier has acknowledged (or its wait has run out).
  *
  * Parity: library/src/reverse_offload/queue_proxy.hpp:40-131 (queue_element_t with
  * the valid flag on its own cache line, 512-slot rings), commands_types.hpp:29-48
@@ -76,6 +80,7 @@ typedef struct {
   bshmem_proxy_desc_t* slots;        /* [capacity], host memory visible to the producer */
   volatile uint64_t* completion;     /* [capacity]: ticket + 1 when executed            */
   volatile uint64_t* result;         /* [capacity]: fetched value / status              */
+  volatile uint64_t* consumed;       /* [capacity]: ticket + 1 once a blocking producer has read its result */
   volatile uint64_t* read_index;     /* consumer progress, for back-pressure            */
   unsigned long long* write_index;   /* ticket counter in the producers' memory         */
   unsigned long long timeout_ns;

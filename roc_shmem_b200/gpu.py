@@ -94,6 +94,11 @@ def cuda_lib() -> C.CDLL:
         f("bshmem_gpu_swarm_get", _I, _VP, _VP, _VP, _U64, _I, _I, _I)
         f("bshmem_gpu_api_selftest", _I, _VP, _VP, _VP, _VP, _I, _VP)
         f("bshmem_gpu_wg_collectives", _I, _VP, _VP, _VP, _I, C.POINTER(_I))
+        f("bshmem_gpu_bench_amo_rate", _I, _VP, _VP, _I, _I, _I, _I, _I, C.POINTER(_U64))
+        f("bshmem_gpu_put_signal_stream", _I, _VP, _VP, _VP, _VP, _U64, _I, _I, _I, _I)
+        f("bshmem_gpu_api_matrix", _I, _VP, _VP, _I, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _VP)
+        f("bshmem_gpu_bind_thread_ctx", _I, _VP, _I)
+        f("bshmem_gpu_get_device", _I, _VP, C.POINTER(_I))
         _declared = True
     return lib
 
@@ -190,8 +195,9 @@ class DeviceRuntime(Runtime):
 
     def rma_kernel(self, sym: torch.Tensor, local: torch.Tensor, pe: int, *, put: bool = True, scope: str = "block",
                    ctas: int = 32, threads: int = 512, nbytes: Optional[int] = None) -> None:
-        """Device-initiated put/get striped over `ctas` CTAs (enqueued, not synchronised)."""
-        sc = {"thread": 0, "warp": 1, "block": 2}[scope]
+        """Device-initiated put/get striped over `ctas` CTAs (enqueued, not synchronised).  Scope "bulk" moves the
+        data with bulk async copies through shared memory (16-byte aligned addresses and size)."""
+        sc = {"thread": 0, "warp": 1, "block": 2, "bulk": 3}[scope]
         n = nbytes if nbytes is not None else local.numel() * local.element_size()
         self._check(self.lib.bshmem_gpu_rma_kernel(self.h, sym.data_ptr(), local.data_ptr(), n, pe, int(put), sc, ctas,
                                                    threads))
@@ -200,6 +206,19 @@ class DeviceRuntime(Runtime):
         return t.data_ptr() - int(self.lib.bshmem_heap_base(self.h))
 
     # ---- device-API micro-benchmarks / functional kernels (csrc/cuda/p2p_kernels.cu) ----
+    def bench_amo_rate(self, target: torch.Tensor, peer: int, iters: int, ctas: int, threads: int) -> float:
+        """8-byte fetch-adds from ctas x threads threads on distinct words of `peer`; returns million atomics / s."""
+        ns = C.c_uint64(0)
+        self._check(self.lib.bshmem_gpu_bench_amo_rate(self.h, target.data_ptr(), target.numel(), peer, iters, ctas, threads,
+                                                       C.byref(ns)))
+        return ctas * threads * iters / max(ns.value, 1) * 1e3
+
+    def put_signal_stream(self, data: torch.Tensor, src: torch.Tensor, sig: torch.Tensor, nbytes: int, peer: int, iters: int,
+                          ctas: int, threads: int = 512) -> None:
+        """Enqueue `iters` one-way putmem_signal(ADD 1) of nbytes striped over ctas CTAs (not synchronised)."""
+        self._check(self.lib.bshmem_gpu_put_signal_stream(self.h, data.data_ptr(), src.data_ptr(), sig.data_ptr(), nbytes, peer,
+                                                          iters, ctas, threads))
+
     def bench_pingpong(self, flag: torch.Tensor, peer: int, iters: int, initiator: bool) -> float:
         """p + wait_until ping-pong with `peer`; returns one-way latency in microseconds."""
         ns = C.c_uint64(0)
@@ -238,6 +257,39 @@ class DeviceRuntime(Runtime):
         self._check(self.lib.bshmem_gpu_api_selftest(self.h, si.data_ptr(), su.data_ptr(), sf.data_ptr(), peer, res.data_ptr()))
         out = res.tolist()
         self.barrier_all()
+        return out[:out.index(-1)]
+
+    def bind_thread(self, ctx=None) -> None:
+        """Run everything the calling thread issues from now on (collectives and waits included) on host context
+        `ctx`'s stream, completing each call before it returns; None unbinds.  Used by service threads that must not
+        queue behind the PE stream."""
+        self._check(self.lib.bshmem_gpu_bind_thread_ctx(self.h, -1 if ctx is None else self._ctx(ctx)))
+
+    def api_matrix_buffers(self, nbytes: int = 4096) -> dict:
+        """Symmetric and local buffers of `api_matrix` (a collective allocation: every PE calls it)."""
+        return {"si": self.zeros((4,), torch.int32), "su": self.zeros((4,), torch.int64), "sf": self.zeros((4,), torch.float32),
+                "data": self.zeros((3 * nbytes,), torch.uint8), "coll": self.zeros((2 * 64 * 16,), torch.float32),
+                "local": torch.zeros(6 * nbytes, dtype=torch.uint8, device=self.device), "nbytes": nbytes}
+
+    def api_matrix(self, bufs: dict, team=None, peer: int = 0, proxy: bool = False) -> list[int]:
+        """The device API matrix (p/g, 15 atomics, put/get at every scope, put_signal, fence/quiet, work-group
+        collectives) through a context of `team` (None = world), PE numbers relative to that team; with `proxy` every
+        operation goes through the reverse-offload ring.  Every member of the team must make the same call.
+        Returns one 1/0 per check."""
+        ring = None
+        if proxy:
+            if getattr(self, "proxy", None) is None:
+                raise ShmemError(5, "api_matrix(proxy=True) needs a runtime initialised with backend='proxy'")
+            ring = self.proxy.ring_dev
+        for k in ("si", "su", "sf"):
+            bufs[k].zero_()
+        slot = 0 if team is None else team.slot
+        res = torch.full((64,), -2, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        self._check(self.lib.bshmem_gpu_api_matrix(self.h, ring, slot, bufs["si"].data_ptr(), bufs["su"].data_ptr(),
+                                                   bufs["sf"].data_ptr(), bufs["data"].data_ptr(), bufs["local"].data_ptr(),
+                                                   bufs["coll"].data_ptr(), bufs["nbytes"], peer, res.data_ptr()))
+        out = res.tolist()
         return out[:out.index(-1)]
 
     def wg_collectives(self, dst: torch.Tensor, src: torch.Tensor) -> int:

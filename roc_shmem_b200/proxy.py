@@ -104,11 +104,12 @@ class Proxy:
         code = D.code_of(src.dtype)
         return D.from_bits(code, self.submit(Desc(op=OP_G, pe=pe, dtype=code, sym_off=self._off(src))))
 
-    def amo(self, op: int, dest, value=0, cond=0, pe: int = 0):
+    def amo(self, op: int, dest, value=0, cond=0, pe: int = 0, blocking: bool = True):
+        """One of the 15 atomics through the ring; a non-blocking submission returns nothing (use non-fetching ops)."""
         code = D.code_of(dest.dtype)
         r = self.submit(Desc(op=OP_AMO, pe=pe, dtype=code, sub_op=op, sym_off=self._off(dest), value=D.to_bits(code, value),
-                             cond=D.to_bits(code, cond)))
-        return D.from_bits(code, r)
+                             cond=D.to_bits(code, cond)), blocking=blocking)
+        return D.from_bits(code, r) if blocking else None
 
     def put_signal(self, dest, src, sig, value: int, pe: int, sig_op: int = D.SIGNAL_SET) -> None:
         loc, fl = self._local(src)

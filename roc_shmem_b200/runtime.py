@@ -117,6 +117,16 @@ class Context:
     def quiet(self):
         self.rt.quiet(self)
 
+    def put_signal(self, dest, src, sig, value, pe, **kw):
+        return self.rt.put_signal(dest, src, sig, value, pe, ctx=self, **kw)
+
+    def __getattr__(self, name):
+        # the atomic family: ctx.atomic_fetch_add(dest, value, pe) == rt.atomic_fetch_add(dest, value, pe, ctx=ctx)
+        if name.startswith("atomic_"):
+            fn = getattr(self.rt, name)
+            return lambda *a, **kw: fn(*a, ctx=self, **kw)
+        raise AttributeError(name)
+
 
 class Runtime:
     def __init__(self, lib: C.CDLL, handle: int, *, tensor_from_ptr: Callable, device: torch.device,

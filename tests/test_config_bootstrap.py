@@ -12,7 +12,7 @@ from roc_shmem_b200.config import Config
 
 def test_config_defaults_env_aliases_and_overrides(monkeypatch):
     c = Config.from_env()
-    assert c.heap_bytes == 1 << 30 and c.max_teams == 40 and c.backend == "auto" and c.nvls == "off"
+    assert c.heap_bytes == 1 << 30 and c.max_teams == 40 and c.backend == "auto" and c.nvls == "auto"
     monkeypatch.setenv("ROC_SHMEM_HEAP_SIZE", "64M")           # the reference's spelling is accepted
     monkeypatch.setenv("B200SHMEM_MAX_NUM_TEAMS", "8")
     monkeypatch.setenv("B200SHMEM_DEBUG", "1")

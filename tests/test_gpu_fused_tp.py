@@ -44,7 +44,7 @@ def test_fused_tp_single_pe():
 def test_fused_tp_two_pes_against_nccl():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200SHMEM_NVLS="off", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29533", "-m", "roc_shmem_b200.bench.tp_bench", "--small", "--iters", "3"]
     p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=280)

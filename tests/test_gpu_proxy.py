@@ -38,3 +38,24 @@ def test_device_commands_through_the_ring_and_host_fault_injection():
     finally:
         rt.proxy.stop()
         shmem.finalize()
+
+
+@pytest.mark.parametrize("backend", ["device", "proxy"])
+def test_device_api_matrix_single_pe(backend):
+    """The whole device API matrix on one PE (peer = self): direct transport and through the ring, world context and
+    a team context (a team over the single PE has its own slot, so the team paths run)."""
+    import roc_shmem_b200 as shmem
+    rt = shmem.init(backend, rank=0, world_size=1, heap_bytes=256 << 20, timeout_ms=5000, proxy_slots=128)
+    try:
+        bufs = rt.api_matrix_buffers(2048)
+        use_proxy = backend == "proxy"
+        checks = rt.api_matrix(bufs, peer=0, proxy=use_proxy)
+        assert len(checks) == 31 and all(c == 1 for c in checks), (checks, rt.error_record())
+        team = rt.team_split_strided(None, 0, 1, 1)
+        checks = rt.api_matrix(bufs, team=team, peer=0, proxy=use_proxy)
+        assert len(checks) == 31 and all(c == 1 for c in checks), (checks, rt.error_record())
+        team.destroy()
+    finally:
+        if backend == "proxy":
+            rt.proxy.stop()
+        shmem.finalize()

@@ -116,3 +116,28 @@ def test_dropped_descriptor_times_out_only_that_command():
         assert px.counters()["dropped"] == 1
         px.stop()
     run_threads(1, body, heap_bytes=1 << 20)
+
+
+def test_full_ring_gives_up_without_leaving_a_hole():
+    """A producer that times out on a FULL ring must not have taken a ticket: the consumer runs strictly in ticket
+    order and would otherwise wait for ever for a slot nobody fills.  Pause the service thread, fill the ring with
+    non-blocking commands, let further submissions time out, resume: everything queued and everything later runs."""
+    def body(rt):
+        px = Proxy(rt, capacity=4, timeout_ms=100)
+        ctr = rt.zeros((1,), torch.int64)
+        px.pause(True)
+        for _ in range(4):                                     # exactly fills the ring; nothing is consumed
+            px.amo(D.AMO_ADD, ctr, 1, 0, 0, blocking=False)
+        for _ in range(3):
+            with pytest.raises(shmem.ShmemTimeout):
+                px.amo(D.AMO_ADD, ctr, 100, 0, 0, blocking=False)   # no room: gives up, reserves nothing
+        px.pause(False)
+        px.set_timeout_ms(10000)
+        for _ in range(10):                                    # later operations all complete, in order
+            px.amo(D.AMO_ADD, ctr, 1, 0, 0)
+        px.quiet()
+        assert int(ctr[0]) == 14                               # the 3 abandoned submissions never ran
+        c = px.counters()
+        assert c["processed"] >= 15 and c["errors"] == 0
+        px.stop()
+    run_threads(1, body, heap_bytes=1 << 20)

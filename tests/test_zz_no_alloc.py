@@ -55,9 +55,20 @@ def test_noalloc_group_collective_matches_allocating_entry_twice():
             st = fn(handles, 4, 0, gpu.COLL_REDUCE, D.code_of(dtype), op, 0, d_off, s_off, n, 3)
             assert st == 0, lib.bshmem_gpu_noalloc_last_error().decode()
             torch.cuda.synchronize()
+            # plain PyTorch fp32 reference of the same reduction over the four sources
+            stack = torch.stack([x.float() for x in src])
+            exact = stack.sum(0) if op == D.SUM else stack.max(0).values
             for r, o in zip(ref, out):
+                assert torch.allclose(o.float(), exact, rtol=2e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-5)
                 assert torch.allclose(o.float(), r.float(), rtol=2e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-6)
                 assert torch.equal(o, r)      # same algorithm, same order: identical bits
+            if call == 1:
+                # the entry allocates nothing: a repeat of the call leaves the device's free memory where it was
+                free_before, _ = torch.cuda.mem_get_info()
+                st = fn(handles, 4, 0, gpu.COLL_REDUCE, D.code_of(dtype), op, 0, d_off, s_off, n, 3)
+                assert st == 0, lib.bshmem_gpu_noalloc_last_error().decode()
+                free_after, _ = torch.cuda.mem_get_info()
+                assert free_after == free_before
         # data movement through the same entry: alltoall pattern (value identifies source PE and block)
         blk = 1000
         a_src = group.empty((blk * 4,), torch.int32)
@@ -72,6 +83,20 @@ def test_noalloc_group_collective_matches_allocating_entry_twice():
         for i in range(4):
             for j in range(4):
                 assert bool((a_dst[i][j * blk:(j + 1) * blk] == (j << 16) + i).all())
+    finally:
+        group.close()
+
+
+def test_noalloc_rejects_ranges_outside_the_heap():
+    from roc_shmem_b200 import gpu
+    group = gpu.LocalGroup(2, heap_bytes=32 << 20)
+    try:
+        fn = _declare(group.lib)
+        handles = (C.c_void_p * 2)(*[rt.h.value for rt in group.pes])
+        heap = int(group.lib.bshmem_gpu_heap_bytes(group.heaps[0]))
+        st = fn(handles, 2, 0, gpu.COLL_FCOLLECT, 0, 0, 0, heap - 64, 4096, 1024, 1)     # destination runs past the heap
+        assert st == 4                                         # BSHMEM_ERR_RANGE, nothing was launched
+        assert "outside" in group.lib.bshmem_gpu_noalloc_last_error().decode()
     finally:
         group.close()
 
