@@ -20,9 +20,10 @@ def expert_ffn(xe: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.T
     return (Fn.silu(xe @ w1.t()) * (xe @ w3.t())) @ w2.t()
 
 
-def moe_reference_single(x, wr, w1, w3, w2, topk, compute_dtype=torch.float32):
-    """All experts local (no communication): plain PyTorch, differentiable.  w1/w3: [E, F, H], w2: [E, H, F]."""
-    idx, w = route(x.detach(), wr, topk)
+def moe_reference_single(x, wr, w1, w3, w2, topk, compute_dtype=torch.float32, router_grad=False):
+    """All experts local (no communication): plain PyTorch, differentiable.  w1/w3: [E, F, H], w2: [E, H, F].
+    With `router_grad` the routing weights stay in the autograd graph (gradients reach `wr` and, through the router, `x`)."""
+    idx, w = route(x if router_grad else x.detach(), wr, topk)
     out = torch.zeros(x.shape, dtype=compute_dtype, device=x.device)
     xc = x.to(compute_dtype)
     for e in range(w1.shape[0]):

@@ -63,7 +63,7 @@ def main() -> None:
         T, H, F = args.tokens, 4096, 14336
     G = E // P
     cap_rows = int(T * topk * P / E * 1.25)
-    heap = (G * cap_rows * H * 2) + 2 * (T * topk * H * 2) + (512 << 20)
+    heap = 2 * (G * cap_rows * H * 2) + 2 * (T * topk * H * 2) + (512 << 20)
     rt = shmem.init("device", device=local, heap_bytes=heap, timeout_ms=20000)
     dev = rt.device
     torch.manual_seed(7)                                   # same weights on every rank, sliced per rank
@@ -124,6 +124,66 @@ def main() -> None:
         with torch.no_grad():
             ms_bf = timed(lambda: base(x), max(2, args.iters // 2), rt)
         res.update({"ms_fwd_bwd_nccl_cublas": ms_b, "ms_fwd_nccl_cublas": ms_bf, "speedup_fwd_bwd": ms_b / ms, "speedup_fwd": ms_bf / ms_f})
+    # ---- the all-to-all alone: dispatch (tokens -> experts) and combine (expert rows -> sources) against
+    # NCCL all_to_all_single moving the same rows; device time of the exchange only, max over ranks ----
+    import ctypes as C
+    from roc_shmem_b200.ops.moe import SIG_FWD_COMBINE, SIG_FWD_DISPATCH, _stream
+    lib = layer.lib
+    n_entries = T * topk
+
+    def a2a_ours(iters):
+        td = tc = 0.0
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for _ in range(iters):
+            layer.route(x)                                   # new call parity, counts exchanged, arrival words armed
+            par, s = layer.parity, _stream()
+            rt.barrier_all()
+            evs[0].record()
+            lib.bshmem_moe_dispatch(C.byref(layer.state), C.byref(layer.plan), x.data_ptr(), 0, layer.topk_idx.data_ptr(),
+                                    layer.pos.data_ptr(), n_entries, topk, H, layer.recv.data_ptr(), layer.meta.data_ptr(), par,
+                                    SIG_FWD_DISPATCH, layer.ctas, s)
+            lib.bshmem_moe_wait_arrivals(C.byref(layer.plan), par, SIG_FWD_DISPATCH, layer.expect_from.data_ptr(), 20000,
+                                         layer.err_word, s)
+            evs[1].record()
+            rt.barrier_all()
+            evs[2].record()
+            lib.bshmem_moe_combine_send(C.byref(layer.state), C.byref(layer.plan), layer.recv.data_ptr(), layer.meta.data_ptr(), H,
+                                        layer.ybuf.data_ptr(), par, SIG_FWD_COMBINE, layer.ctas, s)
+            lib.bshmem_moe_wait_arrivals(C.byref(layer.plan), par, SIG_FWD_COMBINE, layer.send_to.data_ptr(), 20000,
+                                         layer.err_word, s)
+            evs[3].record()
+            torch.cuda.synchronize()
+            td += evs[0].elapsed_time(evs[1])
+            tc += evs[2].elapsed_time(evs[3])
+        t = torch.tensor([td / iters, tc / iters], device=dev)
+        if P > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    a2a_ours(1)
+    ms_disp, ms_comb = a2a_ours(args.iters)
+    layer.check()
+    link_bytes = n_entries * (P - 1) / P * H * 2
+    res.update({"a2a_dispatch_ms": ms_disp, "a2a_combine_ms": ms_comb, "a2a_link_ms_at_770GBps": link_bytes / 770e9 * 1e3,
+                "a2a_dispatch_frac_of_link": (link_bytes / 770e9 * 1e3) / ms_disp if P > 1 else None,
+                "a2a_combine_frac_of_link": (link_bytes / 770e9 * 1e3) / ms_comb if P > 1 else None})
+    if P > 1 and not args.no_baseline:
+        # the same rows through NCCL: sorted by destination expert, split sizes from the routing
+        idx = layer.topk_idx.view(T, topk).long()
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        send = x[order // topk].contiguous()
+        counts = torch.bincount(flat_e, minlength=E)
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts)
+        in_splits = counts.view(P, G).sum(1).tolist()
+        out_splits = recv_counts.view(P, G).sum(1).tolist()
+        recv_n = torch.empty((sum(out_splits), H), dtype=x.dtype, device=dev)
+        back_n = torch.empty_like(send)
+        ms_nd = timed(lambda: dist.all_to_all_single(recv_n, send, out_splits, in_splits), args.iters, rt)
+        ms_nc = timed(lambda: dist.all_to_all_single(back_n, recv_n, in_splits, out_splits), args.iters, rt)
+        res.update({"a2a_dispatch_ms_nccl": ms_nd, "a2a_combine_ms_nccl": ms_nc, "a2a_dispatch_speedup": ms_nd / ms_disp,
+                    "a2a_combine_speedup": ms_nc / ms_comb})
     okt = torch.tensor([int(ok)], device=dev)
     dist.all_reduce(okt, op=dist.ReduceOp.MIN)
     res["all_ranks_ok"] = bool(okt.item())

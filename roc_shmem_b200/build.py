@@ -101,6 +101,22 @@ def build_host(force: bool = False) -> Path:
     return out
 
 
+def build_sanitizer_driver(kind: str, force: bool = False) -> Path:
+    """The host runtime and its native stress driver (csrc/host/sanitize_main.cc) as one executable built with
+    -fsanitize=<kind> ("thread" or "address"): data races and memory errors in the allocator, the team table, the
+    CPU backend and the reverse-offload ring show up when the driver runs (tests/test_host_sanitizers.py)."""
+    if kind not in ("thread", "address"):
+        raise ValueError("kind must be 'thread' or 'address'")
+    LIB.mkdir(exist_ok=True)
+    out = LIB / f"bshmem_sanitize_{kind}"
+    srcs = [CSRC / s for s in HOST_SOURCES] + [CSRC / "host/sanitize_main.cc"]
+    if force or _stale(out, srcs):
+        cmd = ["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={kind}", "-o", str(out)] + \
+            [str(s) for s in srcs] + ["-lpthread", "-lrt", "-ldl"]
+        _run(cmd, LIB / f"bshmem_sanitize_{kind}.build.log")
+    return out
+
+
 def _compile_object(nvcc: str, src: Path, obj: Path, extra: list[str], force: bool) -> str:
     if force or _stale(obj, [src]):
         flags = [f for f in NVCC_FLAGS if f != "-shared"]
@@ -146,7 +162,12 @@ def build_all(force: bool = False, cuda: bool = True) -> dict[str, str]:
     return built
 
 
-if __name__ == "__main__":
+def main() -> int:
     res = build_all(force="--force" in sys.argv)
     for k, v in res.items():
         print(f"{k}: {v}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

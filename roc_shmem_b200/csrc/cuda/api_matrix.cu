@@ -73,7 +73,7 @@ struct MatrixArgs {
     results[r++] = A::ctx_atomic_fetch<float>(s, ctx, m.sym_f, peer) == 2.5f;                                                 \
     A::ctx_fence(s, ctx);                                                                                                     \
   }                                                                                                                           \
-  r = 21;                                                                                                                     \
+  r = 16;                                                                                                                     \
   /* ---- RMA at block, warp and thread scope: put local[0:n) -> peer, get it back into local[k*n..), compare ---- */         \
   for (int i = tid; i < n; i += blockDim.x) m.local[i] = (char)(i * 7 + 3 + team.my_idx);                                     \
   if (tid == 0) block_ok = 1;                                                                                                 \

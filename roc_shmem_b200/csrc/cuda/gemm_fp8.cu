@@ -196,19 +196,22 @@ struct FSmem {
   __device__ __forceinline__ volatile int* abort_flag() const {
     return reinterpret_cast<volatile int*>(gen + FSMEM_TILES + 8 * (2 * FSTAGES + 4) + 8);
   }
-  // reduce-scatter variant: how many epilogue warps have completed their store of the tile with this parity
-  __device__ __forceinline__ int* rs_count(int parity) const {
-    return reinterpret_cast<int*>(gen + FSMEM_TILES + 8 * (2 * FSTAGES + 4) + 16) + parity;
+  // reduce-scatter variant: epilogue warps that have completed their store of a tile, counted monotonically on the
+  // counter (tile ordinal & 3)
+  __device__ __forceinline__ unsigned int* rs_count(int which) const {
+    return reinterpret_cast<unsigned int*>(gen + FSMEM_TILES + 8 * (2 * FSTAGES + 4) + 16) + which;
   }
 };
 
 // Called by lane 0 of an epilogue warp once its own TMA store of a tile is complete: the last of the 16 warps to
-// arrive publishes the whole tile with ONE system-scope fence and ONE signal (no warp ever waits for another; the
-// epilogue warps stay within one k-block of each other, so two alternating counters are enough).
-__device__ __forceinline__ void rs_publish(int* count, uint64_t* sig) {
+// arrive publishes the whole tile with ONE system-scope fence and ONE signal; no warp ever waits for another.
+// The counters only ever grow (a multiple of 16 means "tile complete") and there are four of them, indexed by the
+// tile ordinal: the two partial-product buffers bound the skew between epilogue warps to two k-blocks, which is at
+// most two tiles even when a tile is a single k-block, and a warp publishes one tile late, so the tiles that can be
+// in the publishing stage at the same time are at most three apart and never share a counter.
+__device__ __forceinline__ void rs_publish(unsigned int* count, uint64_t* sig) {
   __threadfence();
-  if (atomicAdd(count, 1) == FEPI_WARPS - 1) {
-    *reinterpret_cast<volatile int*>(count) = 0;
+  if (((atomicAdd(count, 1u) + 1u) & (FEPI_WARPS - 1)) == 0u) {
     ptx::fence_proxy_async_all();
     ptx::fence_acq_rel_sys();
     ptx::red_release_sys_add_u64(sig, 1);
@@ -233,8 +236,7 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
 
   if (threadIdx.x == 0) {
     *L.abort_flag() = 0;
-    *L.rs_count(0) = 0;
-    *L.rs_count(1) = 0;
+    for (int i = 0; i < 4; ++i) *L.rs_count(i) = 0;
     for (int s = 0; s < FSTAGES; ++s) { ptx::mbar_init(L.full(s), 1); ptx::mbar_init(L.empty(s), 1); }
     for (int b = 0; b < 2; ++b) { ptx::mbar_init(L.part_full(b), 1); ptx::mbar_init(L.part_empty(b), FEPI_WARPS); }
     ptx::fence_mbar_init();
@@ -321,7 +323,7 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
     const int quarter = warp & 3;          // TMEM lanes 32*quarter.. belong to this warp
     const int cg = ew >> 2;                // columns [64*cg, 64*cg + 64) of the tile
     uint64_t* pend_sig = nullptr;          // reduce-scatter variant: signal word of the tile whose store is in flight
-    int pend_par = 0, tiles_done = 0;      // ... and which of the two arrival counters that tile uses
+    int pend_par = 0, tiles_done = 0;      // ... and which of the four arrival counters that tile uses
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -360,7 +362,6 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
         ptx::tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * FBN + cg * 64;
         const float2 sc = make_float2(s0, s0);
-#ifndef BSHMEM_FP8_DIAG_NO_PROMOTE      // diagnostic build: tensor-core + TMA pipeline alone (wrong results)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t v[16];
@@ -370,9 +371,6 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
           for (int i = 0; i < 8; ++i)
             acc[c * 8 + i] = __ffma2_rn(sc, make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), acc[c * 8 + i]);
         }
-#else
-        acc[0].x += sc.x + __uint_as_float(taddr);
-#endif
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(L.part_empty(buf));
@@ -417,7 +415,7 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
           ptx::tma_commit_group();
           // the tile's signal is sent once every warp's store is complete: at the next tile's output stage
           pend_sig = reinterpret_cast<uint64_t*>(rs->sig_remote[owner] + (size_t)m_in * cp.num_n_blocks + n_blk);
-          pend_par = tiles_done & 1;
+          pend_par = tiles_done & 3;
         }
       }
       ++tiles_done;

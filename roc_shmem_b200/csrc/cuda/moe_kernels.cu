@@ -288,9 +288,12 @@ __global__ void __launch_bounds__(256) k_combine_send(State st, MoePlanDev pl, c
 }
 
 // out[token] = sum_k w[entry] * ybuf[entry]   (entries over capacity contribute nothing)
+// With `dlog` (backward pass only): out[token] += sum_k dlog[entry] * wr[expert of entry] — the gradient that reaches
+// the layer input through the router logits, added here so that d_x is written once.
 template <bool kWeighted>
 __global__ void k_combine_reduce(MoePlanDev pl, const bf16* __restrict__ ybuf, const float* __restrict__ w, const int* __restrict__ topk_idx,
-                                 const int* __restrict__ pos, int T, int topk, int H, bf16* __restrict__ out) {
+                                 const int* __restrict__ pos, int T, int topk, int H, bf16* __restrict__ out,
+                                 const float* __restrict__ dlog = nullptr, const bf16* __restrict__ wr = nullptr) {
   const int token = blockIdx.x;
   if (token >= T) return;
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
@@ -309,6 +312,20 @@ __global__ void k_combine_reduce(MoePlanDev pl, const bf16* __restrict__ ybuf, c
         float2 f = __bfloat1622float2(h[q]);
         acc[2 * q] += wk * f.x;
         acc[2 * q + 1] += wk * f.y;
+      }
+    }
+    if (dlog != nullptr) {
+      for (int k = 0; k < topk; ++k) {
+        const int i = token * topk + k;
+        const float g = dlog[i];
+        uint4 wv = __ldg(reinterpret_cast<const uint4*>(wr + (size_t)topk_idx[i] * H) + v);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float2 f = __bfloat1622float2(h[q]);
+          acc[2 * q] += g * f.x;
+          acc[2 * q + 1] += g * f.y;
+        }
       }
     }
     uint4 o;
@@ -341,6 +358,80 @@ __global__ void k_router_weight_grad(MoePlanDev pl, const bf16* __restrict__ ybu
   }
   acc = warp_sum(acc);
   if (lane == 0) dw[i] = acc;
+}
+
+// Router backward.  The routing weights are a softmax over the chosen experts' logits (softmax over all experts,
+// renormalised over the top-k), so only the chosen logits receive a gradient:
+//   d_logit[entry k] = w_k * (d_w_k - sum_j w_j * d_w_j)
+__global__ void k_router_dlogits(const float* __restrict__ w, const float* __restrict__ dw, int T, int topk, float* __restrict__ dlog) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float s = 0.f;
+  for (int k = 0; k < topk; ++k) s += w[t * topk + k] * dw[t * topk + k];
+  for (int k = 0; k < topk; ++k) dlog[t * topk + k] = w[t * topk + k] * (dw[t * topk + k] - s);
+}
+
+// d_Wr[e, :] += sum over the CTA's tokens routed to e of d_logit * x[token, :]   (fp32 accumulation, atomics across CTAs).
+// A CTA takes kTok tokens and 2048 columns; its (token, k) entries are first bucketed by expert in shared memory, so
+// the loads of the hit rows can be issued back to back.
+constexpr int kDwrTok = 128;
+__global__ void __launch_bounds__(256) k_router_dwr(const bf16* __restrict__ x, const int* __restrict__ topk_idx, const float* __restrict__ dlog,
+                                                   int T, int H, int E, int topk, float* __restrict__ dwr) {
+  __shared__ int cnt[64], start[65], fill[64];
+  __shared__ int ent[kDwrTok * 8];
+  const int t0 = blockIdx.x * kDwrTok;
+  const int nt = min(kDwrTok, T - t0);
+  const int n_ent = nt * topk;
+  if (threadIdx.x < 64) { cnt[threadIdx.x] = 0; fill[threadIdx.x] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_ent; i += blockDim.x) atomicAdd(&cnt[topk_idx[t0 * topk + i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int a = 0;
+    for (int e = 0; e < E; ++e) { start[e] = a; a += cnt[e]; }
+    start[E] = a;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_ent; i += blockDim.x) {
+    const int e = topk_idx[t0 * topk + i];
+    ent[start[e] + atomicAdd(&fill[e], 1)] = i;
+  }
+  __syncthreads();
+  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (col >= H) return;
+  for (int e = 0; e < E; ++e) {
+    const int b = start[e], n = start[e + 1] - b;
+    if (n == 0) continue;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int j0 = 0; j0 < n; j0 += 4) {
+      uint4 xv[4];
+      float g[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = ent[b + min(j0 + u, n - 1)];
+        g[u] = j0 + u < n ? dlog[t0 * topk + i] : 0.f;
+        xv[u] = *reinterpret_cast<const uint4*>(x + (size_t)(t0 + i / topk) * H + col);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&xv[u]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float2 f = __bfloat1622float2(h[q]);
+          acc[2 * q] += g[u] * f.x;
+          acc[2 * q + 1] += g[u] * f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&dwr[(size_t)e * H + col + j], acc[j]);
+  }
+}
+
+__global__ void k_f32_to_bf16(const float* __restrict__ in, bf16* __restrict__ out, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = __float2bfloat16_rn(in[i]);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -487,6 +578,32 @@ int bshmem_moe_combine_reduce(const MoePlanDev* pl, const void* ybuf, const floa
                               int H, void* out, void* stream) {
   if (w) k_combine_reduce<true><<<T, 256, 0, (cudaStream_t)stream>>>(*pl, (const bf16*)ybuf, w, topk_idx, pos, T, topk, H, (bf16*)out);
   else k_combine_reduce<false><<<T, 256, 0, (cudaStream_t)stream>>>(*pl, (const bf16*)ybuf, nullptr, topk_idx, pos, T, topk, H, (bf16*)out);
+  RT_TRY(cudaGetLastError());
+  return 0;
+}
+
+// The same reduction for the backward pass's closing step, plus the router term (see k_combine_reduce).
+int bshmem_moe_combine_reduce_router(const MoePlanDev* pl, const void* ybuf, const int* topk_idx, const int* pos, int T, int topk, int H,
+                                     void* out, const float* dlog, const void* wr, void* stream) {
+  k_combine_reduce<false><<<T, 256, 0, (cudaStream_t)stream>>>(*pl, (const bf16*)ybuf, nullptr, topk_idx, pos, T, topk, H, (bf16*)out, dlog,
+                                                                (const bf16*)wr);
+  RT_TRY(cudaGetLastError());
+  return 0;
+}
+
+// Router backward: d_logits of the chosen experts [T * topk] from the routing weights and their gradient, then
+// d_Wr [E, H] = d_logits^T · x (accumulated in the fp32 scratch `dwr_f32`, which this call clears first) as bf16.
+int bshmem_moe_router_backward(const void* x, const int* topk_idx, const float* topk_w, const float* dtopk_w, int T, int H, int E, int topk,
+                               float* dlog, float* dwr_f32, void* dwr, void* stream) {
+  if (E > 64 || topk > 8 || H % 8) { g_err = "router backward: at most 64 experts, top-8, H % 8 == 0"; return 1; }
+  cudaStream_t st = (cudaStream_t)stream;
+  k_router_dlogits<<<(T + 255) / 256, 256, 0, st>>>(topk_w, dtopk_w, T, topk, dlog);
+  RT_TRY(cudaGetLastError());
+  RT_TRY(cudaMemsetAsync(dwr_f32, 0, sizeof(float) * (size_t)E * H, st));
+  dim3 grid((T + kDwrTok - 1) / kDwrTok, (H + 2047) / 2048);
+  k_router_dwr<<<grid, 256, 0, st>>>((const bf16*)x, topk_idx, dlog, T, H, E, topk, dwr_f32);
+  RT_TRY(cudaGetLastError());
+  k_f32_to_bf16<<<64, 256, 0, st>>>(dwr_f32, (bf16*)dwr, (size_t)E * H);
   RT_TRY(cudaGetLastError());
   return 0;
 }

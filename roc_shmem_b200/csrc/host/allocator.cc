@@ -28,7 +28,8 @@ bool Bin::take(uint64_t offset) { return free_.erase(offset) != 0; }
 
 uint64_t Pow2BuddyAllocator::round_up_pow2(uint64_t v, uint64_t min_block) {
   uint64_t b = min_block;
-  while (b < v) b <<= 1;
+  // stop at the top bit: a request above 2^63 has no power of two to round up to (the caller's size check rejects it)
+  while (b < v && b < (1ull << 63)) b <<= 1;
   return b;
 }
 
@@ -78,6 +79,7 @@ uint64_t Pow2BuddyAllocator::alloc_aligned(uint64_t bytes, uint64_t alignment) {
   std::lock_guard<std::mutex> g(mu_);
   if (bytes == 0) return kNoOffset;
   if (alignment == 0 || (alignment & (alignment - 1)) != 0) return kNoOffset;
+  if (std::max(bytes, alignment) > heap_bytes_) { ++n_failed_; return kNoOffset; }   // can never fit (and bounds the rounding)
   // A block is aligned to its own size, so asking for max(bytes, alignment)
   // rounded to a power of two satisfies the alignment.
   uint64_t block = round_up_pow2(std::max(bytes, alignment), min_block_);

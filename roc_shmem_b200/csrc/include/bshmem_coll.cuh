@@ -187,46 +187,63 @@ template <typename T> union Vec16 {
 };
 
 // 16-byte vectors [v0, v1) of the reduction, striped over the block.  NS bounds the member count at compile
-// time, U vectors per thread are in flight together: all U x nsrc loads are issued before the first use.
+// time, U vectors per thread form a batch: all U x nsrc loads of a batch are issued before its first use, and the
+// NEXT batch's loads are issued before the current batch is reduced and stored (two register sets), so a thread
+// keeps up to 2 x U x nsrc 16-byte loads in flight across loop iterations.
+template <typename T, int NS, int U>
+__device__ __forceinline__ void reduce_vec_load(Vec16<T> (&in)[U][NS], const uint4* const (&sp)[NS], int nsrc, size_t base, size_t v1) {
+  const size_t tid = threadIdx.x, nth = blockDim.x;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const size_t v = base + u * nth + tid;
+    if (v < v1) {
+#pragma unroll
+      for (int k = 0; k < NS; ++k)
+        if (k < nsrc) in[u][k].raw = sp[k][v];
+    }
+  }
+}
 template <typename T, int OP, int NS, int U>
-__device__ __forceinline__ void reduce_vec_body(int nsrc, const T* const* srcs, int ndst, T* const* dsts, size_t v0, size_t v1) {
+__device__ __forceinline__ void reduce_vec_store(const Vec16<T> (&in)[U][NS], int nsrc, int ndst, T* const* dsts, size_t base, size_t v1) {
   using A = typename Acc<T>::type;
   constexpr int VE = 16 / sizeof(T);
   const size_t tid = threadIdx.x, nth = blockDim.x;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const size_t v = base + u * nth + tid;
+    if (v < v1) {
+      A acc[VE];
+#pragma unroll
+      for (int e = 0; e < VE; ++e) acc[e] = to_acc<T>(in[u][0].e[e]);
+#pragma unroll
+      for (int k = 1; k < NS; ++k) {
+        if (k < nsrc) {
+#pragma unroll
+          for (int e = 0; e < VE; ++e) acc[e] = apply<A>(OP, acc[e], to_acc<T>(in[u][k].e[e]));
+        }
+      }
+      Vec16<T> out;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) out.e[e] = from_acc<T>(acc[e]);
+      for (int d = 0; d < ndst; ++d) reinterpret_cast<uint4*>(dsts[d])[v] = out.raw;
+    }
+  }
+}
+template <typename T, int OP, int NS, int U>
+__device__ __forceinline__ void reduce_vec_body(int nsrc, const T* const* srcs, int ndst, T* const* dsts, size_t v0, size_t v1) {
+  const size_t step = (size_t)U * blockDim.x;
   const uint4* sp[NS];
 #pragma unroll
   for (int k = 0; k < NS; ++k) sp[k] = reinterpret_cast<const uint4*>(srcs[k < nsrc ? k : 0]);
-  for (size_t base = v0; base < v1; base += (size_t)U * nth) {
-    Vec16<T> in[U][NS];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const size_t v = base + u * nth + tid;
-      if (v < v1) {
-#pragma unroll
-        for (int k = 0; k < NS; ++k)
-          if (k < nsrc) in[u][k].raw = sp[k][v];
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const size_t v = base + u * nth + tid;
-      if (v < v1) {
-        A acc[VE];
-#pragma unroll
-        for (int e = 0; e < VE; ++e) acc[e] = to_acc<T>(in[u][0].e[e]);
-#pragma unroll
-        for (int k = 1; k < NS; ++k) {
-          if (k < nsrc) {
-#pragma unroll
-            for (int e = 0; e < VE; ++e) acc[e] = apply<A>(OP, acc[e], to_acc<T>(in[u][k].e[e]));
-          }
-        }
-        Vec16<T> out;
-#pragma unroll
-        for (int e = 0; e < VE; ++e) out.e[e] = from_acc<T>(acc[e]);
-        for (int d = 0; d < ndst; ++d) reinterpret_cast<uint4*>(dsts[d])[v] = out.raw;
-      }
-    }
+  if (v0 >= v1) return;
+  Vec16<T> a[U][NS], b[U][NS];
+  reduce_vec_load<T, NS, U>(a, sp, nsrc, v0, v1);
+  for (size_t base = v0; base < v1; base += 2 * step) {
+    if (base + step < v1) reduce_vec_load<T, NS, U>(b, sp, nsrc, base + step, v1);
+    reduce_vec_store<T, OP, NS, U>(a, nsrc, ndst, dsts, base, v1);
+    if (base + step >= v1) break;
+    if (base + 2 * step < v1) reduce_vec_load<T, NS, U>(a, sp, nsrc, base + 2 * step, v1);
+    reduce_vec_store<T, OP, NS, U>(b, nsrc, ndst, dsts, base + step, v1);
   }
 }
 
@@ -258,8 +275,8 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
                         (std::is_same<T, float>::value || std::is_same<T, double>::value || std::is_same<T, __half>::value ||
                          std::is_same<T, __nv_bfloat16>::value || std::is_same<T, int32_t>::value || std::is_same<T, long long>::value);
   if constexpr (kHot) {
-    // members x unroll = 16 independent 16-byte loads per thread (64 registers; the reduction kernels run 256-thread
-    // blocks, so nothing spills): with ~100 blocks several megabytes are in flight, which NVLink's latency needs
+    // members x unroll = 16 independent 16-byte loads per batch and two batches in flight (128 registers; the
+    // reduction kernels run 256-thread blocks, so nothing spills): ~100 blocks keep tens of megabytes in flight
     if (nsrc <= 2) reduce_vec_body<T, OP, 2, 8>(nsrc, srcs, ndst, dsts, v0, v1);
     else if (nsrc <= 4) reduce_vec_body<T, OP, 4, 4>(nsrc, srcs, ndst, dsts, v0, v1);
     else if (nsrc <= 8) reduce_vec_body<T, OP, 8, 2>(nsrc, srcs, ndst, dsts, v0, v1);

@@ -31,7 +31,7 @@ class MixtralMoEBlock(MoELayer):
 
 class _MoEFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w13, w2, block):
+    def forward(ctx, x, w13, w2, wr, block):
         ctx.block = block
         return block.forward(x).clone()
 
@@ -39,22 +39,23 @@ class _MoEFn(torch.autograd.Function):
     def backward(ctx, dy):
         block = ctx.block
         dx = block.backward(dy.contiguous())
-        return dx.clone(), block.dw13.clone(), block.dw2.clone(), None
+        return dx.clone(), block.dw13.clone(), block.dw2.clone(), block.dwr.clone(), None
 
 
 class MixtralMoEModule(torch.nn.Module):
-    """``torch.nn.Module`` face: expert weights are parameters aliasing the block's buffers; the router is
-    applied without gradient (its weights' gradient needs the softmax backward, which callers that train
-    the router take from ``block.dtopk_w``)."""
+    """``torch.nn.Module`` face: expert and router weights are parameters aliasing the block's buffers; the backward
+    pass returns gradients for all of them and for the input (expert path plus the path through the router's
+    softmax over the chosen experts)."""
 
     def __init__(self, rt, **kw):
         super().__init__()
         self.block = MixtralMoEBlock(rt, training=True, **kw)
         self.w13 = torch.nn.Parameter(self.block.w13)
         self.w2 = torch.nn.Parameter(self.block.w2)
+        self.wr = torch.nn.Parameter(self.block.wr)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return _MoEFn.apply(x, self.w13, self.w2, self.block)
+        return _MoEFn.apply(x, self.w13, self.w2, self.wr, self.block)
 
     def after_step(self) -> None:
         self.block.sync_transposes()

@@ -49,6 +49,8 @@ def moe_lib() -> C.CDLL:
         f("bshmem_moe_combine_send", PS, PP, VP, VP, I, VP, I, I, I, VP)
         f("bshmem_moe_combine_reduce", PP, VP, VP, VP, VP, I, I, I, VP, VP)
         f("bshmem_moe_router_weight_grad", PP, VP, VP, VP, VP, I, I, I, VP, VP)
+        f("bshmem_moe_router_backward", VP, VP, VP, VP, I, I, I, I, VP, VP, VP, VP)
+        f("bshmem_moe_combine_reduce_router", PP, VP, VP, VP, I, I, I, VP, VP, VP, VP)
         f("bshmem_moe_swiglu_fwd", VP, VP, I, I, I, VP, VP)
         f("bshmem_moe_swiglu_bwd", VP, VP, VP, I, I, I, VP, VP)
         f("bshmem_moe_transpose_pad", VP, VP, I, I, I, VP, VP)
@@ -155,7 +157,7 @@ class MoELayer:
         self.dropped = torch.zeros((1,), dtype=torch.int32, device=dev)
         self.arrive = rt.zeros((2 * 4 * P,), torch.int64)
         # ---- symmetric data buffers ----
-        self.recv = rt.empty((G * cap, H), bf, align=1024)                    # dispatched tokens / dispatched grads
+        self.recv = rt.empty((G * cap, H), bf, align=1024)                    # dispatched tokens (kept for dW13 in training)
         self.meta = rt.empty((G * cap,), torch.int32)
         self.ybuf = rt.empty((n_entries, H), bf, align=1024)                  # expert outputs per entry, back at the source
         # ---- expert-side activations ----
@@ -164,7 +166,10 @@ class MoELayer:
         self.yexp = torch.empty((G * cap, H), dtype=bf, device=dev)
         self.out = torch.empty((T, H), dtype=bf, device=dev)
         if training:
-            self.xsave = torch.empty((G * cap, H), dtype=bf, device=dev)      # dispatched inputs kept for dW13
+            # the backward pass dispatches gradients into a receive buffer of its own, so the forward's dispatched
+            # inputs stay where they landed until dW13 has read them (no copy)
+            self.recv_bwd = rt.empty((G * cap, H), bf, align=1024)
+            self.xsave = self.recv
             self.w13_t = torch.empty((G, H, 2 * F), dtype=bf, device=dev)
             self.w2_t = torch.empty((G, F, H), dtype=bf, device=dev)
             self.dh = torch.empty((G * cap, F), dtype=bf, device=dev)
@@ -178,6 +183,10 @@ class MoELayer:
             self.dxbuf = rt.empty((n_entries, H), bf, align=1024)
             self.dx = torch.empty((T, H), dtype=bf, device=dev)
             self.dtopk_w = torch.empty((n_entries,), dtype=torch.float32, device=dev)
+            self.dlogit = torch.empty((n_entries,), dtype=torch.float32, device=dev)   # gradient of the chosen experts' logits
+            self.dwr_f32 = torch.empty((n_experts, H), dtype=torch.float32, device=dev)
+            self.dwr = torch.empty((n_experts, H), dtype=bf, device=dev)             # router weight gradient
+            self._x_in = None
         self.plan = PlanDev(P=P, E=n_experts, me=rt.my_pe, cap=self.cap, base_me=self.base_me.data_ptr(),
                             src_start=self.src_start.data_ptr(), recv_count=self.recv_count.data_ptr(),
                             expect_from=self.expect_from.data_ptr(), send_to=self.send_to.data_ptr(),
@@ -237,7 +246,7 @@ class MoELayer:
                          timeout_ms=self.timeout_ms)
             self._chk(lib.bshmem_moe_swiglu_fwd(self.gu.data_ptr(), self.recv_count.data_ptr(), G, cap, F, self.hact.data_ptr(), s),
                       "swiglu")
-            self.xsave.copy_(self.recv)                            # the receive buffer is reused by the backward dispatch
+            self._x_in = x                                         # the router's backward needs the layer input
         else:
             grouped_gemm(self.recv, self.w13.view(G * 2 * F, H), self.hact, G, rows=self.recv_count, gated=True,
                          arrive=self._sig_ptr(par, SIG_FWD_DISPATCH), expected=self.expect_from, n_arrive=P,
@@ -255,8 +264,9 @@ class MoELayer:
         return self.out[:T]
 
     def backward(self, dout: torch.Tensor) -> torch.Tensor:
-        """Gradients w.r.t. the layer input (returned), the expert weights (self.dw13, self.dw2) and the routing
-        weights (self.dtopk_w).  Must follow forward() of the same tokens."""
+        """Gradients w.r.t. the layer input (returned; expert path and router path), the expert weights (self.dw13,
+        self.dw2), the routing weights (self.dtopk_w) and, through the softmax over the chosen experts, the router
+        weights (self.dwr).  Must follow forward() of the same tokens; the forward's input must still be intact."""
         assert self.training
         lib, T, s = self.lib, dout.shape[0], _stream()
         n_entries = T * self.topk
@@ -266,22 +276,28 @@ class MoELayer:
         self._chk(lib.bshmem_moe_router_weight_grad(C.byref(self.plan), self.ybuf.data_ptr(), dout.data_ptr(),
                                                     self.topk_idx.data_ptr(), self.pos.data_ptr(), n_entries, self.topk, H,
                                                     self.dtopk_w.data_ptr(), s), "router weight grad")
-        # combine-backward = dispatch of w * d_out into the experts' receive buffers (same slots as forward)
+        # router backward: d_logits of the chosen experts and d_Wr = d_logits^T · x
+        self._chk(lib.bshmem_moe_router_backward(self._x_in.data_ptr(), self.topk_idx.data_ptr(), self.topk_w.data_ptr(),
+                                                 self.dtopk_w.data_ptr(), T, H, self.E, self.topk, self.dlogit.data_ptr(),
+                                                 self.dwr_f32.data_ptr(), self.dwr.data_ptr(), s), "router backward")
+        self.launches += 2
+        # combine-backward = dispatch of w * d_out into the experts' gradient receive buffers (same slots as forward)
+        dy = self.recv_bwd
         self._chk(lib.bshmem_moe_dispatch(C.byref(self.state), C.byref(self.plan), dout.data_ptr(), self.topk_w.data_ptr(),
-                                          self.topk_idx.data_ptr(), self.pos.data_ptr(), n_entries, self.topk, H, self.recv.data_ptr(),
+                                          self.topk_idx.data_ptr(), self.pos.data_ptr(), n_entries, self.topk, H, dy.data_ptr(),
                                           0, par, SIG_BWD_DISPATCH, self.ctas, s), "dispatch(bwd)")
         # d_hact = d_y · W2            (B operand = W2^T [F, H], K = H)
-        grouped_gemm(self.recv, self.w2_t.view(G * F, H), self.dh, G, rows=rc, arrive=self._sig_ptr(par, SIG_BWD_DISPATCH),
+        grouped_gemm(dy, self.w2_t.view(G * F, H), self.dh, G, rows=rc, arrive=self._sig_ptr(par, SIG_BWD_DISPATCH),
                      expected=self.expect_from, n_arrive=P, timeout_ms=self.timeout_ms)
         # dW2 = d_y^T · hact: token-major operands straight into the MN-major tensor-core path
         if self.tn_gemm:
-            zero_pad_rows(self.recv, G, rc)
+            zero_pad_rows(dy, G, rc)
             zero_pad_rows(self.hact, G, rc)
-            grouped_gemm_tn(self.recv, self.hact, self.dw2.view(G * H, F), G, rc, timeout_ms=self.timeout_ms)
+            grouped_gemm_tn(dy, self.hact, self.dw2.view(G * H, F), G, rc, timeout_ms=self.timeout_ms)
         else:                          # explicit transposes + ragged-K K-major GEMM
             ta = self.t_a[: G * H * cap].view(G * H, cap)
             tb = self.t_b[: G * F * cap].view(G * F, cap)
-            self._chk(lib.bshmem_moe_transpose_pad(self.recv.data_ptr(), rc.data_ptr(), G, cap, H, ta.data_ptr(), s), "transpose")
+            self._chk(lib.bshmem_moe_transpose_pad(dy.data_ptr(), rc.data_ptr(), G, cap, H, ta.data_ptr(), s), "transpose")
             self._chk(lib.bshmem_moe_transpose_pad(self.hact.data_ptr(), rc.data_ptr(), G, cap, F, tb.data_ptr(), s), "transpose")
             grouped_gemm(ta, tb, self.dw2.view(G * H, F), G, fixed_rows=H, klen=rc, timeout_ms=self.timeout_ms)
         # SwiGLU backward, then dW13 = d_gu^T · x and d_x = d_gu · W13
@@ -304,8 +320,10 @@ class MoELayer:
                                               self.dxbuf.data_ptr(), par, SIG_BWD_COMBINE, self.ctas, s), "combine_send(bwd)")
         self._chk(lib.bshmem_moe_wait_arrivals(C.byref(self.plan), par, SIG_BWD_COMBINE, self.send_to.data_ptr(), self.timeout_ms,
                                                self.err_word, s), "wait")
-        self._chk(lib.bshmem_moe_combine_reduce(C.byref(self.plan), self.dxbuf.data_ptr(), 0, self.topk_idx.data_ptr(),
-                                                self.pos.data_ptr(), T, self.topk, H, self.dx.data_ptr(), s), "combine_reduce(bwd)")
+        # d_x = sum over k of the returned rows + the router path (d_logits · Wr), written once
+        self._chk(lib.bshmem_moe_combine_reduce_router(C.byref(self.plan), self.dxbuf.data_ptr(), self.topk_idx.data_ptr(),
+                                                       self.pos.data_ptr(), T, self.topk, H, self.dx.data_ptr(),
+                                                       self.dlogit.data_ptr(), self.wr.data_ptr(), s), "combine_reduce(bwd)")
         return self.dx[:T]
 
     def check(self) -> None:

@@ -22,19 +22,19 @@ def main() -> None:
     # world context, PE numbers are world numbers
     rt.barrier_all()
     checks = rt.api_matrix(bufs, team=None, peer=(me + 1) % n, proxy=use_proxy)
-    assert len(checks) == 31 and all(c == 1 for c in checks), f"[pe {me}] world ctx {backend}: {checks} {rt.error_record()}"
+    assert len(checks) == 25 and all(c == 1 for c in checks), f"[pe {me}] world ctx {backend}: {checks} {rt.error_record()}"
     rt.barrier_all()
     # a team with its own slot over all PEs in reverse... (start 0, stride 1, size n) and, with 4+ PEs, the even PEs
     team = rt.team_split_strided(None, 0, 1, n)
     checks = rt.api_matrix(bufs, team=team, peer=(team.my_pe + 1) % team.n_pes, proxy=use_proxy)
-    assert len(checks) == 31 and all(c == 1 for c in checks), f"[pe {me}] team ctx {backend}: {checks} {rt.error_record()}"
+    assert len(checks) == 25 and all(c == 1 for c in checks), f"[pe {me}] team ctx {backend}: {checks} {rt.error_record()}"
     rt.barrier_all()
     team.destroy()
     if n >= 4:
         even = rt.team_split_strided(None, 0, 2, n // 2)
         if even.valid:
             checks = rt.api_matrix(bufs, team=even, peer=(even.my_pe + 1) % even.n_pes, proxy=use_proxy)
-            assert len(checks) == 31 and all(c == 1 for c in checks), f"[pe {me}] even-team ctx {backend}: {checks}"
+            assert len(checks) == 25 and all(c == 1 for c in checks), f"[pe {me}] even-team ctx {backend}: {checks}"
         rt.barrier_all()
         if even.valid:
             even.destroy()

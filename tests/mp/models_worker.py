@@ -73,7 +73,8 @@ def main() -> None:
     moe.check()
     xall = torch.cat(xs).float().requires_grad_(True)
     w2r = w2.float().requires_grad_(True)
-    ref2, idx, _ = moe_reference_single(xall, wr, w1.float(), w3.float(), w2r, topk)
+    wrr = wr.float().requires_grad_(True)
+    ref2, idx, _ = moe_reference_single(xall, wrr, w1.float(), w3.float(), w2r, topk, router_grad=True)
     ref2.backward(torch.cat(dys).float())
     mine = slice(me * T, (me + 1) * T)
     same = (moe.topk_idx.view(T, topk).long() == idx[mine]).all(-1)
@@ -82,6 +83,10 @@ def main() -> None:
     assert (dx2.float() - xall.grad[mine])[same].abs().max().item() <= 5e-2 * xall.grad.abs().max().item() + 3e-2, "moe dx"
     # expert weight gradients sum over all ranks' tokens; tokens whose routing flipped on a near-tie perturb them slightly
     assert (moe.dw2.float() - w2r.grad[es]).abs().max().item() <= 8e-2 * w2r.grad.abs().max().item() + 5e-2, "moe dw2"
+    # router weights: every rank holds the gradient of its own tokens; the sum over ranks is the full gradient
+    dwr_all = moe.dwr.float().clone()
+    dist.all_reduce(dwr_all)
+    assert (dwr_all - wrr.grad).abs().max().item() <= 8e-2 * wrr.grad.abs().max().item() + 5e-2, "moe dwr"
     rt.barrier_all()
     print(f"MODELS_OK {me}", flush=True)
     shmem.finalize()

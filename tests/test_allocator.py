@@ -56,6 +56,16 @@ def test_round_up(lib):
     assert lib.bshmem_unit_round_up_pow2((1 << 30) - 1, 128) == 1 << 30
 
 
+def test_absurd_sizes_fail_fast(lib):
+    """A size above 2^63 has no power of two to round up to: the request must fail, not loop (the heap lock is held)."""
+    assert lib.bshmem_unit_round_up_pow2((1 << 63) + 1, 128) == 1 << 63
+    a = lib.bshmem_unit_alloc_create(1 << 20, 0, 128)
+    for size in ((1 << 64) - 1, (1 << 63) + 1, 1 << 62, (1 << 20) + 1):
+        assert lib.bshmem_unit_alloc(a, size, 0) == NO
+    assert lib.bshmem_unit_alloc(a, 1 << 20, 0) != NO                 # the heap itself still works
+    lib.bshmem_unit_alloc_destroy(a)
+
+
 def test_binner_roots_are_naturally_aligned(lib):
     a = lib.bshmem_unit_alloc_create(1 << 30, 4 << 20, 128)
     offs, sizes = (C.c_uint64 * 64)(), (C.c_uint64 * 64)()

@@ -105,10 +105,13 @@ def test_mixtral_block_autograd(rt):
     mod.block.check()
     xr = x.detach().float().requires_grad_(True)
     w2r = w2.float().requires_grad_(True)
-    ref, idx, _ = moe_reference_single(xr, wr, w1.float(), w3.float(), w2r, topk)
+    wrr = wr.float().requires_grad_(True)
+    ref, idx, _ = moe_reference_single(xr, wrr, w1.float(), w3.float(), w2r, topk, router_grad=True)
     ref.backward(dy.float())
     same = (mod.block.topk_idx.view(T, topk).long() == idx).all(-1)
     assert same.float().mean() > 0.99
     assert (y.float() - ref.detach())[same].abs().max().item() <= 3e-2 * ref.abs().max().item() + 2e-2
     assert (x.grad.float() - xr.grad)[same].abs().max().item() <= 5e-2 * xr.grad.abs().max().item() + 2e-2
     assert (mod.w2.grad.float() - w2r.grad).abs().max().item() <= 5e-2 * w2r.grad.abs().max().item() + 5e-2
+    # the router's weights get their gradient through the softmax over the chosen experts
+    assert (mod.wr.grad.float() - wrr.grad).abs().max().item() <= 8e-2 * wrr.grad.abs().max().item() + 5e-2

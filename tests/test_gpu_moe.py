@@ -128,7 +128,8 @@ def test_moe_forward_backward_single_pe(rt, training, tn_gemm):
     layer.check()
     xr = x.float().requires_grad_(True)
     w1r, w3r, w2r = (t.float().requires_grad_(True) for t in (w1, w3, w2))
-    ref, idx, w = moe_reference_single(xr, wr, w1r, w3r, w2r, topk)
+    wrr = wr.float().requires_grad_(True)
+    ref, idx, w = moe_reference_single(xr, wrr, w1r, w3r, w2r, topk, router_grad=True)
     # routing must agree for an element-wise comparison; compare tokens whose routing matches
     same = (layer.topk_idx.view(T, topk).long() == idx).all(-1)
     assert same.float().mean() > 0.99
@@ -150,3 +151,7 @@ def test_moe_forward_backward_single_pe(rt, training, tn_gemm):
         assert (layer.dw13[g].float() - ref13).abs().max().item() <= 5e-2 * s13 + 5e-2, g
         s2 = w2r.grad[g].abs().max().item()
         assert (layer.dw2[g].float() - w2r.grad[g]).abs().max().item() <= 5e-2 * s2 + 5e-2, g
+    # router weights: gradient through the softmax over the chosen experts (tokens whose routing differs from the
+    # reference's contribute differently; they are < 1 % of the rows, so compare with a matching tolerance)
+    sr = wrr.grad.abs().max().item()
+    assert (layer.dwr.float() - wrr.grad).abs().max().item() <= 8e-2 * sr + 5e-2

@@ -50,10 +50,10 @@ def test_device_api_matrix_single_pe(backend):
         bufs = rt.api_matrix_buffers(2048)
         use_proxy = backend == "proxy"
         checks = rt.api_matrix(bufs, peer=0, proxy=use_proxy)
-        assert len(checks) == 31 and all(c == 1 for c in checks), (checks, rt.error_record())
+        assert len(checks) == 25 and all(c == 1 for c in checks), (checks, rt.error_record())
         team = rt.team_split_strided(None, 0, 1, 1)
         checks = rt.api_matrix(bufs, team=team, peer=0, proxy=use_proxy)
-        assert len(checks) == 31 and all(c == 1 for c in checks), (checks, rt.error_record())
+        assert len(checks) == 25 and all(c == 1 for c in checks), (checks, rt.error_record())
         team.destroy()
     finally:
         if backend == "proxy":

@@ -1,0 +1,47 @@
+"""A C program builds against the shipped headers and links the host library through `bshmem-config`, the API
+reference generator runs, and the CMake package file names both libraries."""
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+from roc_shmem_b200 import _native, docs, pkgconfig
+
+
+def test_c_consumer_builds_and_runs(tmp_path):
+    _native.host_lib()                                   # make sure the library exists
+    src = tmp_path / "app.c"
+    src.write_text(textwrap.dedent("""
+        #include <stdio.h>
+        #include "bshmem.h"
+        int main(void) {
+          void* world = 0; bshmem_handle_t h = 0;
+          if (bshmem_cpu_world_create(0, 1, 1 << 20, &world) != BSHMEM_OK) return 1;
+          if (bshmem_cpu_init(world, 0, 0, &h) != BSHMEM_OK) return 2;
+          long* x = (long*)bshmem_malloc(h, 8 * sizeof(long));
+          long v = 42;
+          if (!x || bshmem_ctx_putmem(h, BSHMEM_CTX_DEFAULT, x, &v, sizeof v, 0) != BSHMEM_OK || x[0] != 42) return 3;
+          bshmem_free(h, x);
+          bshmem_finalize(h);
+          bshmem_cpu_world_destroy(world);
+          puts("C_CONSUMER_OK");
+          return 0;
+        }"""))
+    p = pkgconfig.paths()
+    exe = tmp_path / "app"
+    cmd = ["gcc", str(src), f"-I{p['includedir']}", f"-L{p['libdir']}", f"-Wl,-rpath,{p['libdir']}", "-lbshmem_host", "-o", str(exe)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "C_CONSUMER_OK" in r.stdout, r.stdout + r.stderr
+
+
+def test_api_reference_and_cmake_package(tmp_path):
+    text = docs.generate()
+    for name in ("bshmem_malloc", "bshmem_team_split_strided", "putmem_signal", "team_reduce", "ctx_atomic_fetch_add",
+                 "bshmem_gpu_group_collective_noalloc"):
+        assert name in text
+    cm = (Path(pkgconfig.paths()["cmakedir"]) / "bshmemConfig.cmake").read_text()
+    assert "bshmem::host" in cm and "bshmem::cuda" in cm
+    out = subprocess.run([sys.executable, "-m", "roc_shmem_b200.pkgconfig", "--cflags", "--libs"], capture_output=True, text=True)
+    assert "-lbshmem_host" in out.stdout and "csrc/include" in out.stdout
