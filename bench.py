@@ -128,6 +128,8 @@ def main() -> int:
         return 2
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    from roc_shmem_b200.utils.affinity import bind_to_gpu
+    bind_to_gpu(local_rank)          # pinned staging buffers on the GPU's own NUMA node (matters when 8 ranks share the host)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)       # the baseline arm's collectives (and the bootstrap store)
     # the fused kernels use plain peer stores and loads; no multicast object is bound for this job

@@ -30,6 +30,7 @@ def main() -> None:
     ap.add_argument("--out", default="")
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--peer", type=int, default=1, help="target PE of the sweep (PE 0 initiates)")
+    ap.add_argument("--one", default="", help="SCOPE:CTAS:BYTES — run only that put a few times (profiler captures, one rank: the target is the PE itself)")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -51,6 +52,15 @@ def main() -> None:
     target = rt.zeros((1,), torch.int64)
     amo_words = rt.zeros((65536,), torch.int64)
     rt.barrier_all()
+    if args.one:
+        scope, ctas, size = args.one.split(":")
+        for _ in range(3):
+            rt.rma_kernel(sym, src, peer, put=True, scope=scope, ctas=int(ctas), threads=128 if scope == "bulk" else 512, nbytes=int(size))
+        rt.quiet()
+        torch.cuda.synchronize()
+        print(json.dumps({"one": args.one, "ok": bool(torch.equal(sym[: int(size)], src[: int(size)])) if n == 1 else None}))
+        shmem.finalize()
+        return
 
     # ---- latency micro-benchmarks (both PEs of the pair participate) ----
     if me in pair and n >= 2:
@@ -103,6 +113,32 @@ def main() -> None:
                     us = e0.elapsed_time(e1) * 1e3 / iters
                     res["bandwidth"].append({"op": op, "scope": scope, "ctas": ctas, "threads": threads, "bytes": size,
                                              "us": round(us, 3), "GBps": round(size / us / 1e3, 2)})
+        # host-initiated put / get (the copy engine moves the bytes): the peer-copy rate the device paths are held against
+        rt.set_blocking(False)
+        for op in ("host_put", "host_get"):
+            for size in [x for x in sizes if x >= (64 << 10)]:
+                iters = args.iters if size <= (16 << 20) else max(3, args.iters // 3)
+
+                def one():
+                    if op == "host_put":
+                        rt.put(sym[:size], src[:size], peer, nbi=True)
+                    else:
+                        rt.get(src[:size], sym[:size], peer, nbi=True)
+                one()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(iters):
+                    one()
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / iters
+                res["bandwidth"].append({"op": op, "scope": "copy_engine", "ctas": 0, "threads": 0, "bytes": size,
+                                         "us": round(us, 3), "GBps": round(size / us / 1e3, 2)})
+        rt.synchronize()
+        rt.set_blocking(True)
+        src.copy_(torch.randint(0, 256, (args.max_bytes,), dtype=torch.uint8,
+                                generator=torch.Generator(device="cpu").manual_seed(0)).to(dev))   # host_get overwrote it
         # one-way putmem_signal bandwidth and 8-byte fetch-add rate as sweeps over the issuing CTAs
         res["put_signal_bandwidth"], res["amo_fetch_add_rate"] = [], []
         sig = sigs[7:8]

@@ -19,13 +19,28 @@ constexpr int kThreads = kReduceThreads;
 #define COLL_CAT2(a, b) a##b
 #define COLL_CAT(a, b) COLL_CAT2(a, b)
 
+// dynamic shared memory of the reduction kernels: the staging ring of coll::reduce_bulk
+#ifndef COLL_UNIT_MOVE
+constexpr uint32_t kDynSmem = coll::kBulkSmemBytes;
+#else
+constexpr uint32_t kDynSmem = 0;
+#endif
+
 template <typename T>
 __device__ int reduce_typed(const State& s, const DTeam& t, const CollArgs& a, int cta, int ncta) {
+  extern __shared__ __align__(128) char coll_dyn_smem[];
+  char* bulk = kDynSmem ? coll_dyn_smem : nullptr;
   T* d = reinterpret_cast<T*>(s.heap_base[s.my_pe] + a.dst_off);
   const T* src = reinterpret_cast<const T*>(s.heap_base[s.my_pe] + a.src_off);
   if (a.kind == BSHMEM_COLL_REDUCE_SCATTER) {
-    if (a.stage_seq) return coll::team_reduce_scatter_staged<T>(s, t, a.op, d, src, a.n, a.stage_seq, cta, ncta);
-    return coll::team_reduce_scatter<T>(s, t, a.op, d, src, a.n, cta, ncta);
+    if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value) {
+      // large sums on the whole world: the switch reduces (see the allreduce below)
+      if (a.use_nvls && s.mc_base && t.size == s.n_pes && a.op == BSHMEM_SUM && ((a.dst_off | a.src_off) & 15) == 0 &&
+          (a.n * sizeof(T)) % 16 == 0 && !a.stage_seq)
+        return coll::team_reduce_scatter_nvls<T>(s, t, d, src, a.n, cta, ncta);
+    }
+    if (a.stage_seq) return coll::team_reduce_scatter_staged<T>(s, t, a.op, d, src, a.n, a.stage_seq, cta, ncta, bulk);
+    return coll::team_reduce_scatter<T>(s, t, a.op, d, src, a.n, cta, ncta, bulk);
   }
   if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value) {
     // the multicast mapping spans every PE, so the in-switch reduction only fits a team that is the whole world
@@ -34,8 +49,8 @@ __device__ int reduce_typed(const State& s, const DTeam& t, const CollArgs& a, i
         (a.n * sizeof(T)) % 16 == 0 && a.ll_epoch == 0 && a.n * sizeof(T) > BSHMEM_LLB_PAYLOAD_BYTES)
       return coll::team_reduce_nvls<T>(s, t, d, src, a.n, cta, ncta);
   }
-  if (a.stage_seq) return coll::team_reduce_staged<T>(s, t, a.op, d, src, a.n, a.stage_seq, cta, ncta);
-  return coll::team_reduce<T>(s, t, a.op, d, src, a.n, cta, ncta, a.ll_epoch);
+  if (a.stage_seq) return coll::team_reduce_staged<T>(s, t, a.op, d, src, a.n, a.stage_seq, cta, ncta, bulk);
+  return coll::team_reduce<T>(s, t, a.op, d, src, a.n, cta, ncta, a.ll_epoch, bulk);
 }
 
 __device__ __noinline__ int run_coll(const State& s, DTeam t, const CollArgs& a, int cta, int ncta) {
@@ -94,7 +109,7 @@ __global__ void __launch_bounds__(kThreads) COLL_CAT(k_coll_group_, COLL_UNIT)(c
 }  // namespace
 
 cudaError_t COLL_CAT(launch_, COLL_UNIT)(const State& s, const DTeam& t, const CollArgs& a, int ctas, int* status, cudaStream_t stream) {
-  COLL_CAT(k_coll_, COLL_UNIT)<<<ctas, kThreads, 0, stream>>>(s, t, a, status);
+  COLL_CAT(k_coll_, COLL_UNIT)<<<ctas, kThreads, kDynSmem, stream>>>(s, t, a, status);
   return cudaGetLastError();
 }
 
@@ -102,13 +117,17 @@ cudaError_t COLL_CAT(launch_group_, COLL_UNIT)(const State* states, const DTeam*
                                                int* status, cudaStream_t stream) {
   CollArgs args_copy = a;
   void* args[] = {&states, &teams, &args_copy, &status};
-  return cudaLaunchCooperativeKernel((void*)COLL_CAT(k_coll_group_, COLL_UNIT), dim3(ctas, n), dim3(kThreads), args, 0, stream);
+  return cudaLaunchCooperativeKernel((void*)COLL_CAT(k_coll_group_, COLL_UNIT), dim3(ctas, n), dim3(kThreads), args, kDynSmem, stream);
 }
 
 void COLL_CAT(preload_, COLL_UNIT)() {
   cudaFuncAttributes fa;
   cudaFuncGetAttributes(&fa, COLL_CAT(k_coll_, COLL_UNIT));
   cudaFuncGetAttributes(&fa, COLL_CAT(k_coll_group_, COLL_UNIT));
+  if (kDynSmem) {      // per device: the caller has made the PE's device current
+    cudaFuncSetAttribute(COLL_CAT(k_coll_, COLL_UNIT), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDynSmem);
+    cudaFuncSetAttribute(COLL_CAT(k_coll_group_, COLL_UNIT), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDynSmem);
+  }
 }
 
 }  // namespace collk

@@ -114,53 +114,14 @@ struct GemmRs : PolicyDefaults {
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
   }
   // Own tile: add the peers' bf16 partials of this 32x64 chunk to the fp32 accumulators, in source order
-  // (fixed, so results are reproducible run to run).  A partial chunk is fetched with fully coalesced 16-byte
-  // loads (lane -> row lane/8 + 4i, piece lane%8), parked in the warp's swizzled staging buffer and read back
-  // row-per-lane; the next partial's loads are in flight meanwhile.
+  // (fixed, so results are reproducible run to run); see gemm::add_partial_chunks.
   __device__ static __forceinline__ void adjust(const Params& p, const Smem& L, EpiState&, const Chunk& ck, float (&f)[64], int ew, int lane) {
     const int owner = ck.m_blk / p.blocks_per_owner;
     if (owner != p.my_rank || p.P == 1) return;
     const long long N = p.core.N;
     const int r_local = ck.row0 - owner * p.rows_per_owner;
-    const int pr = lane >> 3, pc = lane & 7;
-    const uint32_t buf = L.epi(ew);
-    const __nv_bfloat16* src0 = p.staging_local + (long long)(r_local + pr) * N + ck.col0 + pc * 8;
-    const long long slot = (long long)p.rows_per_owner * N;
-    uint4 x[8];
-    int s = p.my_rank == 0 ? 1 : 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] = ptx::ld_relaxed_v4(src0 + s * slot + (long long)(4 * i) * N);
-    while (true) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = pr + 4 * i;
-        const uint32_t dst = buf + row * 128 + ((pc ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(x[i].x), "r"(x[i].y), "r"(x[i].z), "r"(x[i].w) : "memory");
-      }
-      __syncwarp();
-      int next = s + 1;
-      if (next == p.my_rank) ++next;
-      if (next < p.P) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = ptx::ld_relaxed_v4(src0 + next * slot + (long long)(4 * i) * N);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint4 y;
-        const uint32_t a = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(y.x), "=r"(y.y), "=r"(y.z), "=r"(y.w) : "r"(a) : "memory");
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&y);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float2 v = __bfloat1622float2(h[e]);
-          f[j * 8 + 2 * e] += v.x;
-          f[j * 8 + 2 * e + 1] += v.y;
-        }
-      }
-      __syncwarp();
-      if (next >= p.P) break;
-      s = next;
-    }
+    const __nv_bfloat16* src0 = p.staging_local + (long long)(r_local + (lane >> 3)) * N + ck.col0 + (lane & 7) * 8;
+    gemm::add_partial_chunks(f, src0, (long long)p.rows_per_owner * N, N, p.P, p.my_rank, L.epi(ew), lane);
   }
   __device__ static __forceinline__ void tile_end(const Params& p, const Smem&, EpiState& st, const Chunk& ck, int, int) {
     const int owner = ck.m_blk / p.blocks_per_owner;

@@ -156,6 +156,77 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Reduce-scatter epilogues: add the bf16 32x64 chunks of the other PEs' partial results to the warp's 64 fp32
+// accumulators per lane (row = lane), in source order 0..P-1 skipping `skip` (fixed order: reproducible bits).
+// `src0` points at (row lane/8, column 8*(lane%8)) of the chunk in source slot 0, `slot` is the distance between
+// source slots and `ld` the row pitch, both in elements.  A chunk is fetched with fully coalesced 16-byte loads
+// (lane -> row lane/8 + 4i, piece lane%8), parked in the warp's swizzled 4 KiB staging buffer `buf` (free at this
+// point) and read back row-per-lane; the next source's loads are already in flight meanwhile.
+// kPrefetch = true keeps the next source's eight loads in flight while the current one is added (32 more registers);
+// false fetches four at a time and suits kernels that are short of registers.
+template <bool kPrefetch = true>
+__device__ __forceinline__ void add_partial_chunks(float (&f)[64], const __nv_bfloat16* src0, long long slot, long long ld, int P, int skip,
+                                                   uint32_t buf, int lane) {
+  const int pr = lane >> 3, pc = lane & 7;
+  auto park = [&](const uint4& v, int i) {
+    const int row = pr + 4 * i;
+    const uint32_t dst = buf + row * 128 + ((pc ^ (row & 7)) << 4);
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  };
+  auto add_row = [&]() {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint4 y;
+      const uint32_t a = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(y.x), "=r"(y.y), "=r"(y.z), "=r"(y.w) : "r"(a) : "memory");
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 v = __bfloat1622float2(h[e]);
+        f[j * 8 + 2 * e] += v.x;
+        f[j * 8 + 2 * e + 1] += v.y;
+      }
+    }
+  };
+  int s = skip == 0 ? 1 : 0;
+  if (s >= P) return;
+  if constexpr (kPrefetch) {
+    uint4 x[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = ptx::ld_relaxed_v4(src0 + s * slot + (long long)(4 * i) * ld);
+    while (true) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) park(x[i], i);
+      __syncwarp();
+      int next = s + 1;
+      if (next == skip) ++next;
+      if (next < P) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = ptx::ld_relaxed_v4(src0 + next * slot + (long long)(4 * i) * ld);
+      }
+      add_row();
+      __syncwarp();
+      if (next >= P) break;
+      s = next;
+    }
+  } else {
+    for (; s < P; ++s) {
+      if (s == skip) continue;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint4 x[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = ptx::ld_relaxed_v4(src0 + s * slot + (long long)(4 * (half * 4 + i)) * ld);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) park(x[i], half * 4 + i);
+      }
+      __syncwarp();
+      add_row();
+      __syncwarp();
+    }
+  }
+}
+
 // Defaults a policy can inherit.
 struct PolicyDefaults {
   static constexpr bool kWaitStoresPerTile = false;

@@ -68,11 +68,13 @@ struct Fp8Ag {
 };
 
 // Reduce-scatter state (GEMM -> reduce-scatter variant): every PE multiplies its K shard, rounds the 128x256 partial
-// tile to bf16 and TMA-stores it into the staging slot [parity][source PE] of the PE that owns those rows, then bumps
-// the tile's signal word there; after its last tile every CTA sums the P partials of the owned tiles dealt to it.
+// tiles of rows another PE owns to bf16 and TMA-stores them into the staging slot [parity][source PE] of that owner,
+// then bumps the tile's signal word there.  The tiles of its own rows come last: their epilogue waits for the P-1
+// partials that arrived meanwhile, adds them to the fp32 accumulators and writes the result (no reduction pass).
 struct Fp8Rs {
   int P, my_rank, blocks_per_rank, pad;         // blocks_per_rank: 128-row blocks per owner
   CUtensorMap map_stage[kMaxPes];               // owner q's slot for (parity, source = this PE): [M/P, N] bf16
+  CUtensorMap map_out;                          // this PE's reduced rows [M/P, N] (ldo)
   unsigned long long* sig_remote[kMaxPes];      // owner q's signal words [blocks_per_rank * N/256] (monotonic over calls)
   const unsigned long long* sig_local;
   const __nv_bfloat16* stage_local;             // this PE's staging of this call's parity: [P][M/P][N]
@@ -391,6 +393,23 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
         if (lane == 0) ptx::tma_wait_group_read<0>();
       }
       __syncwarp();
+      if constexpr (kRS) {
+        const int owner = m_blk / rs->blocks_per_rank;
+        if (owner == rs->my_rank && rs->P > 1) {
+          // own rows: the P-1 partials of this tile must have landed; add them (source order, fixed) to the accumulators
+          const int m_in = m_blk - owner * rs->blocks_per_rank;
+          int sig_ok = 1;
+          if (lane == 0)
+            sig_ok = wait_ge<true>(rs->sig_local + (size_t)m_in * cp.num_n_blocks + n_blk, (unsigned long long)(rs->P - 1) * rs->call, g,
+                                   ERR_F8_RS_SIGNAL) ? 1 : 0;
+          sig_ok = __shfl_sync(0xffffffffu, sig_ok, 0);
+          if (!sig_ok) { ok = false; break; }
+          const long long N = cp.N;
+          const __nv_bfloat16* src0 = rs->stage_local + (long long)(m_in * FBM + quarter * 32 + (lane >> 3)) * N +
+                                      (long long)n_blk * FBN + cg * 64 + (lane & 7) * 8;
+          add_partial_chunks<false>(reinterpret_cast<float(&)[64]>(acc), src0, (long long)(cp.M / rs->P) * N, N, rs->P, rs->my_rank, L.epi(ew), lane);
+        }
+      }
       const uint32_t rowbase = L.epi(ew) + lane * 128;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -409,13 +428,19 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
         }
       } else {
         if (lane == 0) {
-          // partial chunk -> the owner's staging slot (peer memory), then one signal per warp and tile
           const int owner = m_blk / rs->blocks_per_rank, m_in = m_blk - owner * rs->blocks_per_rank;
-          ptx::tma_store_2d(&rs->map_stage[owner], L.epi(ew), n_blk * FBN + cg * 64, m_in * FBM + quarter * 32);
-          ptx::tma_commit_group();
-          // the tile's signal is sent once every warp's store is complete: at the next tile's output stage
-          pend_sig = reinterpret_cast<uint64_t*>(rs->sig_remote[owner] + (size_t)m_in * cp.num_n_blocks + n_blk);
-          pend_par = tiles_done & 3;
+          if (owner == rs->my_rank) {
+            // the reduced chunk of this PE's own rows goes straight to the output
+            ptx::tma_store_2d(&rs->map_out, L.epi(ew), n_blk * FBN + cg * 64, m_in * FBM + quarter * 32);
+            ptx::tma_commit_group();
+          } else {
+            // partial chunk -> the owner's staging slot (peer memory), then one signal per tile
+            ptx::tma_store_2d(&rs->map_stage[owner], L.epi(ew), n_blk * FBN + cg * 64, m_in * FBM + quarter * 32);
+            ptx::tma_commit_group();
+            // the tile's signal is sent once every warp's store is complete: at the next tile's output stage
+            pend_sig = reinterpret_cast<uint64_t*>(rs->sig_remote[owner] + (size_t)m_in * cp.num_n_blocks + n_blk);
+            pend_par = tiles_done & 3;
+          }
         }
       }
       ++tiles_done;
@@ -432,45 +457,6 @@ __device__ __forceinline__ void gemm_fp8_body(const Fp8Params& prm, const Fp8Rs*
   // ------------------------------ teardown ---------------------------------------
   ptx::tc_fence_before();
   __syncthreads();
-  if constexpr (kRS) {
-    // ---- reduce the partials of the tiles this PE owns: owned tile t goes to CTA t % grid ----
-    const int owned = rs->blocks_per_rank * cp.num_n_blocks;
-    const unsigned long long want = (unsigned long long)rs->P * rs->call;      // one signal per source PE and tile
-    const size_t slot = (size_t)(cp.M / rs->P) * cp.N;           // elements per source slot
-    for (int t = blockIdx.x; t < owned && !*L.abort_flag(); t += gridDim.x) {
-      if (threadIdx.x == 0) wait_ge<true>(rs->sig_local + t, want, g, ERR_F8_RS_SIGNAL);
-      __syncthreads();
-      if (*L.abort_flag()) break;
-      const int m_in = t / cp.num_n_blocks, n_blk = t - m_in * cp.num_n_blocks;
-      // 128 rows x 32 vectors of 8 bf16; the summation order over sources is fixed (0..P-1): reproducible
-      for (int v = threadIdx.x; v < FBM * 32; v += blockDim.x) {
-        const int r = v >> 5, c = (v & 31) * 8;
-        const size_t off = (size_t)(m_in * FBM + r) * cp.N + (size_t)n_blk * FBN + c;
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-        for (int s0 = 0; s0 < rs->P; s0 += 4) {
-          uint4 x[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (s0 + u < rs->P) x[u] = ptx::ld_relaxed_v4(rs->stage_local + (size_t)(s0 + u) * slot + off);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (s0 + u < rs->P) {
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x[u]);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
-            }
-          }
-        }
-        uint4 o;
-        o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
-        o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(rs->out + (size_t)(m_in * FBM + r) * rs->ldo + (size_t)n_blk * FBN + c) = o;
-      }
-    }
-    __syncthreads();
-  }
   if constexpr (kAG) {
     // before the kernel ends, CTA 0 makes sure every peer has finished pulling this PE's rows
     if (!*L.abort_flag() && blockIdx.x == 0 && (int)threadIdx.x < prm.ag.P && (int)threadIdx.x != prm.ag.my_rank)
@@ -834,6 +820,8 @@ int bshmem_fp8_rs_run(void* plan, const void* A8, const float* scale_a, const vo
   r.stage_local = reinterpret_cast<const __nv_bfloat16*>(p->staging_local + (uint64_t)parity * P * slot_bytes);
   r.out = static_cast<__nv_bfloat16*>(out);
   r.ldo = ldo;
+  rc = host::make_tmap_2d(&r.map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, rows, p->N, ldo, 32, 64);
+  if (rc) return rc;
   r.call = p->call;
   int ctas = g_sms[p->device];
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;

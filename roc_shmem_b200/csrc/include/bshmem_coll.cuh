@@ -247,11 +247,96 @@ __device__ __forceinline__ void reduce_vec_body(int nsrc, const T* const* srcs, 
   }
 }
 
+// ---- large reductions through shared memory with bulk async copies ------------------------------------------------
+// Plain loads are bounded by the outstanding-miss capacity of an SM's load/store unit: about 1.3 TB/s of local HBM
+// and a few hundred GB/s over NVLink (3 us latency) however many loads a thread keeps in flight.  Here one thread
+// fetches a chunk of EVERY source with cp.async.bulk (global -> shared, mbarrier completion; sources may be peer
+// memory, nothing is multicast) into a ring of kBulkStages stages, all threads reduce the stage out of shared memory
+// and write the result with ordinary (fire-and-forget) stores to the ndst destinations.
+constexpr int kBulkStages = 3;
+constexpr uint32_t kBulkStageBytes = 48 * 1024;
+constexpr uint32_t kBulkSmemBytes = kBulkStages * kBulkStageBytes + 64;   // + mbarriers
+// Range [begin, end) in elements, both multiples of 16 / sizeof(T); every pointer 16-byte aligned.  Returns false if
+// a bounded wait ran out (the error record is filled).
+template <typename T, int OP>
+__device__ __forceinline__ bool reduce_bulk(const State& s, int nsrc, const T* const* srcs, int ndst, T* const* dsts, size_t begin,
+                                            size_t end, char* smem) {
+  using A = typename Acc<T>::type;
+  constexpr int VE = 16 / sizeof(T);
+  __shared__ int bulk_ok;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBulkStages * kBulkStageBytes);
+  const uint32_t chunk = (kBulkStageBytes / nsrc) & ~127u;            // bytes per source and stage
+  const size_t bytes = (end - begin) * sizeof(T);
+  const size_t nchunks = (bytes + chunk - 1) / chunk;
+  if (threadIdx.x == 0) {
+    bulk_ok = 1;
+    for (int i = 0; i < kBulkStages; ++i)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&bars[i])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  auto issue = [&](size_t c) {           // thread 0: chunk c of every source into stage c % kBulkStages
+    const int st = (int)(c % kBulkStages);
+    const uint32_t nb = (uint32_t)((c + 1) * (size_t)chunk <= bytes ? chunk : bytes - c * (size_t)chunk);
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&bars[st]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nb * (uint32_t)nsrc) : "memory");
+    for (int k = 0; k < nsrc; ++k) {
+      const uint32_t sm = (uint32_t)__cvta_generic_to_shared(smem + (size_t)st * kBulkStageBytes + (size_t)k * chunk);
+      const char* g = reinterpret_cast<const char*>(srcs[k] + begin) + c * (size_t)chunk;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(sm), "l"(g), "r"(nb), "r"(bar) : "memory");
+    }
+  };
+  if (threadIdx.x == 0)
+    for (size_t c = 0; c < nchunks && c < (size_t)kBulkStages; ++c) issue(c);
+  const unsigned long long t0 = dev::timer();
+  for (size_t c = 0; c < nchunks; ++c) {
+    const int st = (int)(c % kBulkStages);
+    const uint32_t parity = (uint32_t)((c / kBulkStages) & 1);
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&bars[st]);
+    uint32_t done = 0, it = 0;
+    while (true) {
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+      if (done) break;
+      if ((++it & 63) == 0 && (bulk_ok == 0 || dev::timer() - t0 > s.timeout_ns)) {
+        if (bulk_ok != 0 && threadIdx.x == 0) dev::record_error(s, BSHMEM_ERR_TIMEOUT, -1, BSHMEM_WHERE_MBARRIER, (uint64_t)srcs[0], c, 0);
+        bulk_ok = 0;
+        break;
+      }
+    }
+    __syncthreads();                       // bulk_ok is the same for everybody from here
+    if (!bulk_ok) break;
+    const uint32_t nb = (uint32_t)((c + 1) * (size_t)chunk <= bytes ? chunk : bytes - c * (size_t)chunk);
+    const char* stage = smem + (size_t)st * kBulkStageBytes;
+    const size_t v_base = (begin * sizeof(T) + c * (size_t)chunk) >> 4;          // 16-byte vector index in the tensors
+    for (uint32_t v = threadIdx.x; v < (nb >> 4); v += blockDim.x) {
+      Vec16<T> in, out;
+      in.raw = *reinterpret_cast<const uint4*>(stage + (size_t)v * 16);
+      A acc[VE];
+#pragma unroll
+      for (int e = 0; e < VE; ++e) acc[e] = to_acc<T>(in.e[e]);
+      for (int k = 1; k < nsrc; ++k) {
+        in.raw = *reinterpret_cast<const uint4*>(stage + (size_t)k * chunk + (size_t)v * 16);
+#pragma unroll
+        for (int e = 0; e < VE; ++e) acc[e] = apply<A>(OP, acc[e], to_acc<T>(in.e[e]));
+      }
+#pragma unroll
+      for (int e = 0; e < VE; ++e) out.e[e] = from_acc<T>(acc[e]);
+      for (int d = 0; d < ndst; ++d) reinterpret_cast<uint4*>(dsts[d])[v_base + v] = out.raw;
+    }
+    __syncthreads();                       // the stage has been read by everybody: refill it
+    if (threadIdx.x == 0 && c + kBulkStages < nchunks) issue(c + kBulkStages);
+  }
+  __syncthreads();
+  return bulk_ok != 0;
+}
+
 // dst[i] = reduce over members k (in team order) of src_k[i], for i in [begin, end) elements;
 // the result goes to `ndst` destinations.  Vector body + scalar edges, striped over the block.
 template <typename T, int OP>
-__device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, int ndst, T* const* dsts,
-                                                size_t begin, size_t end) {
+__device__ __forceinline__ void reduce_range_op(const State& s, int nsrc, const T* const* srcs, int ndst, T* const* dsts,
+                                                size_t begin, size_t end, char* bulk) {
   constexpr int op = OP;      // compile-time operator: the per-element switch in apply() folds away
   using A = typename Acc<T>::type;
   constexpr int VE = 16 / sizeof(T);
@@ -268,7 +353,13 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
     for (int k = 1; k < nsrc; ++k) acc = apply<A>(op, acc, to_acc<T>(srcs[k][i]));
     for (int d = 0; d < ndst; ++d) dsts[d][i] = from_acc<T>(acc);
   }
-  const size_t v0 = vbeg / VE, v1 = vend / VE;
+  size_t v0 = vbeg / VE, v1 = vend / VE;
+  // big aligned ranges go through shared memory with bulk async copies when the kernel provides the buffer
+  if (bulk != nullptr && aligned && (v1 - v0) * 16 >= (size_t)64 * 1024 && nsrc <= 16 &&
+      (OP == BSHMEM_SUM || OP == BSHMEM_MAX || OP == BSHMEM_MIN)) {
+    if (reduce_bulk<T, OP>(s, nsrc, srcs, ndst, dsts, vbeg, vend, bulk)) v0 = v1;     // nothing left for the register path
+    else return;
+  }
   // the unrolled variants exist for the element types and operators of bulk reductions (sum / max / min of
   // float, double, half, bf16, int32, int64); everything else takes the generic body, which keeps the build short
   constexpr bool kHot = (OP == BSHMEM_SUM || OP == BSHMEM_MAX || OP == BSHMEM_MIN) &&
@@ -295,19 +386,20 @@ __device__ __forceinline__ void reduce_range_op(int nsrc, const T* const* srcs, 
 // Run-time operator -> compile-time instantiation (bitwise operators exist for integer types only).
 // Not inlined: one copy per element type is shared by every collective kernel of a translation unit,
 // which keeps the kernels (and their compile time) small; the call happens once per CTA and collective.
+// `bulk`: kBulkSmemBytes of 128-byte aligned dynamic shared memory for the large-range path, or null.
 template <typename T>
-__device__ __noinline__ void reduce_range(int op, int nsrc, const T* const* srcs, int ndst, T* const* dsts,
-                                             size_t begin, size_t end) {
+__device__ __noinline__ void reduce_range(const State& s, int op, int nsrc, const T* const* srcs, int ndst, T* const* dsts,
+                                          size_t begin, size_t end, char* bulk = nullptr) {
   switch (op) {
-    case BSHMEM_SUM: reduce_range_op<T, BSHMEM_SUM>(nsrc, srcs, ndst, dsts, begin, end); break;
-    case BSHMEM_MIN: reduce_range_op<T, BSHMEM_MIN>(nsrc, srcs, ndst, dsts, begin, end); break;
-    case BSHMEM_MAX: reduce_range_op<T, BSHMEM_MAX>(nsrc, srcs, ndst, dsts, begin, end); break;
-    case BSHMEM_PROD: reduce_range_op<T, BSHMEM_PROD>(nsrc, srcs, ndst, dsts, begin, end); break;
+    case BSHMEM_SUM: reduce_range_op<T, BSHMEM_SUM>(s, nsrc, srcs, ndst, dsts, begin, end, bulk); break;
+    case BSHMEM_MIN: reduce_range_op<T, BSHMEM_MIN>(s, nsrc, srcs, ndst, dsts, begin, end, bulk); break;
+    case BSHMEM_MAX: reduce_range_op<T, BSHMEM_MAX>(s, nsrc, srcs, ndst, dsts, begin, end, bulk); break;
+    case BSHMEM_PROD: reduce_range_op<T, BSHMEM_PROD>(s, nsrc, srcs, ndst, dsts, begin, end, bulk); break;
     default:
       if constexpr (!std::is_floating_point<typename Acc<T>::type>::value) {
-        if (op == BSHMEM_AND) reduce_range_op<T, BSHMEM_AND>(nsrc, srcs, ndst, dsts, begin, end);
-        else if (op == BSHMEM_OR) reduce_range_op<T, BSHMEM_OR>(nsrc, srcs, ndst, dsts, begin, end);
-        else reduce_range_op<T, BSHMEM_XOR>(nsrc, srcs, ndst, dsts, begin, end);
+        if (op == BSHMEM_AND) reduce_range_op<T, BSHMEM_AND>(s, nsrc, srcs, ndst, dsts, begin, end, bulk);
+        else if (op == BSHMEM_OR) reduce_range_op<T, BSHMEM_OR>(s, nsrc, srcs, ndst, dsts, begin, end, bulk);
+        else reduce_range_op<T, BSHMEM_XOR>(s, nsrc, srcs, ndst, dsts, begin, end, bulk);
       }
   }
 }
@@ -421,7 +513,7 @@ __device__ __forceinline__ int team_reduce_ll(const State& s, const Team& t, int
 // allreduce (`*_to_all`): dest and source are symmetric; dest may alias source.
 template <typename T>
 __device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
-                                           int cta = 0, int ncta = 1, unsigned long long ll_epoch = 0) {
+                                           int cta = 0, int ncta = 1, unsigned long long ll_epoch = 0, char* bulk = nullptr) {
   // small vectors on the world team: one exchange (the condition is the same on every PE: symmetric addresses)
   if ((n * sizeof(T)) % (sizeof(T) > 4 ? sizeof(T) : 4) == 0 && n > 0 &&
       ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & (sizeof(T) > 4 ? 7 : 3)) == 0) {
@@ -446,13 +538,13 @@ __device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op
     size_t b, e;
     split_range(n, ncta, cta, VE, &b, &e);
     T* mine[1] = {dest};
-    reduce_range<T>(op, t.size, srcs, 1, mine, b, e);
+    reduce_range<T>(s, op, t.size, srcs, 1, mine, b, e);
   } else {
     // two-shot: I own slice my_idx; reduce it from everyone, push the result to everyone
     size_t sb, se, b, e;
     split_range(n, t.size, t.my_idx, VE, &sb, &se);
     split_range(se - sb, ncta, cta, VE, &b, &e);
-    reduce_range<T>(op, t.size, srcs, t.size, dsts, sb + b, sb + e);
+    reduce_range<T>(s, op, t.size, srcs, t.size, dsts, sb + b, sb + e, bulk);
   }
   if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, 0); }
   return team_barrier(s, t, cta);         // results delivered; sources reusable
@@ -461,7 +553,7 @@ __device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op
 // reduce-scatter: dest (n elements) = reduction of the members' source[my_idx*n : (my_idx+1)*n].
 template <typename T>
 __device__ __forceinline__ int team_reduce_scatter(const State& s, const Team& t, int op, T* dest, const T* source,
-                                                   size_t n, int cta = 0, int ncta = 1) {
+                                                   size_t n, int cta = 0, int ncta = 1, char* bulk = nullptr) {
   const T* srcs[BSHMEM_MAX_PES];
   for (int k = 0; k < t.size; ++k) srcs[k] = dev::ptr(s, source, dev::team_pe(t, k)) + (size_t)t.my_idx * n;
   int rc = team_sync(s, t, cta);
@@ -469,8 +561,7 @@ __device__ __forceinline__ int team_reduce_scatter(const State& s, const Team& t
   size_t b, e;
   split_range(n, ncta, cta, 16 / sizeof(T), &b, &e);
   T* mine[1] = {dest};
-  // dest has its own offset; realign the vector path by handing in shifted bases
-  reduce_range<T>(op, t.size, srcs, 1, mine, b, e);
+  reduce_range<T>(s, op, t.size, srcs, 1, mine, b, e, bulk);
   if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, 0); }
   return team_barrier(s, t, cta);
 }
@@ -598,7 +689,7 @@ __device__ __forceinline__ int team_alltoall_staged(const State& s, const Team& 
 // straight from `source`).  n elements per PE; n * sizeof(T) is a multiple of 16 and source is 16-byte aligned.
 template <typename T>
 __device__ __forceinline__ int team_reduce_scatter_staged(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
-                                                          unsigned long long seq, int cta, int ncta) {
+                                                          unsigned long long seq, int cta, int ncta, char* bulk = nullptr) {
   size_t b, e;
   split_range(n, ncta, cta, 16 / sizeof(T), &b, &e);
   const size_t slot = n * sizeof(T);
@@ -614,7 +705,7 @@ __device__ __forceinline__ int team_reduce_scatter_staged(const State& s, const 
   for (int k = 0; k < t.size; ++k)
     srcs[k] = k == t.my_idx ? source + (size_t)t.my_idx * n : reinterpret_cast<const T*>(st + (size_t)k * slot);
   T* mine[1] = {dest};
-  reduce_range<T>(op, t.size, srcs, 1, mine, b, e);
+  reduce_range<T>(s, op, t.size, srcs, 1, mine, b, e, bulk);
   if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, slot); }
   return BSHMEM_OK;
 }
@@ -624,7 +715,7 @@ __device__ __forceinline__ int team_reduce_scatter_staged(const State& s, const 
 // reading their sources, so dest may even alias source) and a closing barrier delivers the results.
 template <typename T>
 __device__ __forceinline__ int team_reduce_staged(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
-                                                  unsigned long long seq, int cta, int ncta) {
+                                                  unsigned long long seq, int cta, int ncta, char* bulk = nullptr) {
   constexpr size_t VE = 16 / sizeof(T);
   const size_t slot = (BSHMEM_STAGE_BYTES / t.size) & ~(size_t)15;   // room per sender; a slice is at most ceil(n / size) elements
   for (int k = 1; k < t.size; ++k) {
@@ -648,7 +739,7 @@ __device__ __forceinline__ int team_reduce_staged(const State& s, const Team& t,
     srcs[k] = k == t.my_idx ? source : reinterpret_cast<const T*>(st + (size_t)k * slot) - sb;
     dsts[k] = dev::ptr(s, dest, dev::team_pe(t, k));
   }
-  reduce_range<T>(op, t.size, srcs, t.size, dsts, sb + b, sb + e);
+  reduce_range<T>(s, op, t.size, srcs, t.size, dsts, sb + b, sb + e, bulk);
   if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, n * sizeof(T)); }
   return team_barrier(s, t, cta);
 }
@@ -696,6 +787,46 @@ __device__ __forceinline__ int team_reduce_nvls(const State& s, const Team& t, T
     }
   }
   return team_barrier(s, t, cta);
+}
+
+// reduce-scatter through the switch: my slice of everybody's source is reduced by one multimem.ld_reduce per vector
+// and stored to the local dest.  fp32 / bf16 sum; n * sizeof(T) a multiple of 16; source and dest 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ int team_reduce_scatter_nvls(const State& s, const Team& t, T* dest, const T* source, size_t n,
+                                                        int cta = 0, int ncta = 1) {
+  static_assert(std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value, "fp32 / bf16 only");
+  constexpr size_t VE = 16 / sizeof(T);
+  int rc = team_sync(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  size_t b, e;
+  split_range(n, ncta, cta, VE, &b, &e);
+  const uint64_t soff = reinterpret_cast<const char*>(source + (size_t)t.my_idx * n) - s.heap_base[s.my_pe];
+  const char* mc_src = s.mc_base + soff;
+  uint4* out = reinterpret_cast<uint4*>(dest);
+  constexpr int U = 8;
+  const size_t v1 = e / VE;
+  for (size_t base = b / VE; base < v1; base += (size_t)U * blockDim.x) {
+    uint4 r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = base + (size_t)u * blockDim.x + threadIdx.x;
+      if (v < v1) {
+        if constexpr (std::is_same<T, float>::value) {
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(r[u].x), "=r"(r[u].y), "=r"(r[u].z), "=r"(r[u].w) : "l"(mc_src + v * 16) : "memory");
+        } else {
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(r[u].x), "=r"(r[u].y), "=r"(r[u].z), "=r"(r[u].w) : "l"(mc_src + v * 16) : "memory");
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = base + (size_t)u * blockDim.x + threadIdx.x;
+      if (v < v1) out[v] = r[u];
+    }
+  }
+  return team_barrier(s, t, cta);       // every member has finished reading everybody's source
 }
 
 // roc_shmem-style names for single-block use ---------------------------------------------------------
