@@ -42,7 +42,7 @@ NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "--use_fast_math", "-Xcompiler",
 # name -> (sources relative to csrc/, extra flags)
 CUDA_TARGETS = {
     "libbshmem_cuda.so": (["cuda/vmm_heap.cu", "cuda/gpu_backend.cu", "cuda/coll_dispatch.cu", "cuda/coll_move.cu", "cuda/coll_reduce_f32.cu",
-                           "cuda/coll_reduce_f16.cu", "cuda/coll_reduce_i32.cu", "cuda/coll_reduce_i8.cu", "cuda/p2p_kernels.cu", "cuda/api_matrix.cu", "cuda/group_noalloc.cu", "cuda/gpu_proxy.cu", "cuda/device_util_kernels.cu"] + HOST_SOURCES, []),
+                           "cuda/coll_reduce_f16.cu", "cuda/coll_reduce_i32.cu", "cuda/coll_reduce_i8.cu", "cuda/p2p_kernels.cu", "cuda/api_matrix.cu", "cuda/functional_tester.cu", "cuda/functional_tester_coll.cu", "cuda/group_noalloc.cu", "cuda/gpu_proxy.cu", "cuda/device_util_kernels.cu"] + HOST_SOURCES, []),
     "libbshmem_gemm.so": (["cuda/gemm_bf16.cu"], []),
     "libbshmem_fused.so": (["cuda/fused_tp.cu"], []),
     "libbshmem_moe.so": (["cuda/moe_kernels.cu", "cuda/moe_gemm.cu"], []),

@@ -399,7 +399,8 @@ class GpuBackend final : public Backend {
       return BSHMEM_ERR_UNSUPPORTED;
     }
     a.psync_off = g.psync_off;
-    a.use_nvls = use_nvls_ ? 1 : 0;
+    // in-switch reductions pay off from four PEs on (with two, pulling the one peer's data is faster)
+    a.use_nvls = (use_nvls_ && (heap_->n_pes > 2 || a.kind == BSHMEM_COLL_FCOLLECT)) ? 1 : 0;
     int ctas = 1;
     if (g.slot >= 0 && bytes > (32u << 10)) {   // one CTA per 32 KiB: remote latency, not bandwidth, bounds a CTA
       ctas = (int)((bytes + (32u << 10) - 1) / (32u << 10));
@@ -432,11 +433,18 @@ class GpuBackend final : public Backend {
         case BSHMEM_COLL_FCOLLECT: case BSHMEM_COLL_ALLTOALL: fits = a.n % 16 == 0; break;
         case BSHMEM_COLL_REDUCE_SCATTER: fits = (a.n * es) % 16 == 0; break;
         // the multicast reduction needs no staging; below the one-shot limit the pull form is a single pass
-        case BSHMEM_COLL_REDUCE: fits = !(use_nvls_ && a.op == BSHMEM_SUM && (a.dtype == BSHMEM_FLOAT || a.dtype == BSHMEM_BF16)) &&
+        case BSHMEM_COLL_REDUCE: fits = !(a.use_nvls && a.op == BSHMEM_SUM && (a.dtype == BSHMEM_FLOAT || a.dtype == BSHMEM_BF16)) &&
                                         bytes > BSHMEM_LLB_PAYLOAD_BYTES; break;
         default: break;
       }
-      if (fits) a.stage_seq = ++stage_seq_;
+      if (fits) {
+        a.stage_seq = ++stage_seq_;
+        // every channel runs its own flag exchange and the kernel ends with the slowest one, so a staged call wants
+        // few, fat channels: 128 KiB each (a block moves that in under 3 us)
+        ctas = (int)((bytes + (128u << 10) - 1) / (128u << 10));
+        if (ctas > coll_ctas_) ctas = coll_ctas_;
+        if (ctas < 1) ctas = 1;
+      }
     }
     RT_TRY(collk::launch(state_, team_of(g), a, ctas, L.dstatus, st));
     if (!blocking_now()) return BSHMEM_OK;

@@ -98,6 +98,8 @@ def cuda_lib() -> C.CDLL:
         f("bshmem_gpu_put_signal_stream", _I, _VP, _VP, _VP, _VP, _U64, _I, _I, _I, _I)
         f("bshmem_gpu_api_matrix", _I, _VP, _VP, _I, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _VP)
         f("bshmem_gpu_bind_thread_ctx", _I, _VP, _I)
+        f("bshmem_gpu_functional_run", _I, _VP, _I, _I, _I, _I, _I, _I, _I, _U64, _VP, _VP, _VP, _VP, _VP, _VP, C.c_long, _I,
+          C.c_uint, C.POINTER(C.c_float))
         f("bshmem_gpu_get_device", _I, _VP, C.POINTER(_I))
         _declared = True
     return lib
@@ -291,6 +293,18 @@ class DeviceRuntime(Runtime):
                                                    bufs["coll"].data_ptr(), bufs["nbytes"], peer, res.data_ptr()))
         out = res.tolist()
         return out[:out.index(-1)]
+
+    def functional_run(self, test_type: int, *, size: int, wgs: int, wg_size: int, loops: int, skip: int, peer: int, sym_a, sym_b,
+                       local, words, timers, status, team=None, ctx_options: int = 0, initiator: bool = True,
+                       n_bins: int = 0) -> float:
+        """One launch of the functional tester's kernel for `test_type` (bench/functional.py holds the table of
+        types and sizes the buffers); returns the CUDA-event time of the timed part in milliseconds."""
+        ms = C.c_float(0.0)
+        self._check(self.lib.bshmem_gpu_functional_run(
+            self.h, test_type, 0 if team is None else team.slot, peer, wgs, wg_size, loops, skip, size, sym_a.data_ptr(),
+            sym_b.data_ptr(), local.data_ptr(), words.data_ptr(), timers.data_ptr(), status.data_ptr(), ctx_options,
+            1 if initiator else 0, n_bins, C.byref(ms)))
+        return ms.value
 
     def wg_collectives(self, dst: torch.Tensor, src: torch.Tensor) -> int:
         st = C.c_int(-1)

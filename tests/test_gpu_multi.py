@@ -73,3 +73,13 @@ def test_device_api_matrix_default_and_team_context(backend):
                   extra_env={"API_MATRIX_BACKEND": backend})
     assert p.returncode == 0, p.stdout[-4000:] + p.stderr[-4000:]
     assert p.stdout.count("API_MATRIX_OK") == 2
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_functional_driver_all_types(nproc):
+    """Every type of the functional test driver between real PEs (sizes to 64 KiB, 4 work-groups of 128 threads)."""
+    _need(nproc)
+    p = _torchrun(nproc, ["-m", "roc_shmem_b200.bench.functional", "--all", "-w", "4", "-z", "128", "--loop", "20", "--skip", "4",
+                          "--loop-large", "6"], 29650 + nproc, timeout=400)
+    assert p.returncode == 0, p.stdout[-4000:] + p.stderr[-4000:]
+    assert '"failed": []' in p.stdout
