@@ -26,6 +26,7 @@ struct CollArgs {
   int use_nvls;
   unsigned long long ll_epoch;   // != 0: epoch of a host-launched low-latency allreduce (same on every PE)
   unsigned long long stage_seq;  // != 0: one-exchange form through the staging region, call number (same on every PE)
+  int stage_oneshot;             // allreduce with stage_seq: 1 = every PE reduces the whole vector (one exchange), 0 = two-shot
 };
 
 // Threads per block: 512 for the data-movement unit; 256 for the reduction units, whose unrolled multi-source loops

@@ -49,6 +49,7 @@ __device__ int reduce_typed(const State& s, const DTeam& t, const CollArgs& a, i
         (a.n * sizeof(T)) % 16 == 0 && a.ll_epoch == 0 && a.n * sizeof(T) > BSHMEM_LLB_PAYLOAD_BYTES)
       return coll::team_reduce_nvls<T>(s, t, d, src, a.n, cta, ncta);
   }
+  if (a.stage_seq && a.stage_oneshot) return coll::team_reduce_staged_oneshot<T>(s, t, a.op, d, src, a.n, a.stage_seq, cta, ncta, bulk);
   if (a.stage_seq) return coll::team_reduce_staged<T>(s, t, a.op, d, src, a.n, a.stage_seq, cta, ncta, bulk);
   return coll::team_reduce<T>(s, t, a.op, d, src, a.n, cta, ncta, a.ll_epoch, bulk);
 }

@@ -425,6 +425,7 @@ class GpuBackend final : public Backend {
     // staging half, 16-byte granular.  Every PE evaluates the same conditions on the same arguments, so the call
     // number (and with it the staging half) is the same everywhere.
     a.stage_seq = 0;
+    a.stage_oneshot = 0;
     if (main_lane && g.slot == 0 && g.set.size == heap_->n_pes && heap_->n_pes > 1 && a.ll_epoch == 0 && bytes >= 16 &&
         bytes + 4096 <= BSHMEM_STAGE_BYTES && ((a.dst_off | a.src_off) & 15) == 0) {
       const uint64_t es = bshmem_dtype_size(a.dtype);
@@ -439,9 +440,16 @@ class GpuBackend final : public Backend {
       }
       if (fits) {
         a.stage_seq = ++stage_seq_;
+        if (a.kind == BSHMEM_COLL_REDUCE) {
+          // one exchange moves (P-1) vectors per PE, two exchanges 2 (P-1)/P: the single exchange wins while the
+          // extra (P-1)(P-2)/P vectors cost less than a flag exchange (about 8 us, i.e. about 5 MiB on the links)
+          const uint64_t P = (uint64_t)heap_->n_pes;
+          const uint64_t slot = (BSHMEM_STAGE_BYTES / P) & ~(uint64_t)15;
+          if (bytes <= slot && bytes * (P - 1) * (P - 2) / P <= (5ull << 20)) a.stage_oneshot = 1;
+        }
         // every channel runs its own flag exchange and the kernel ends with the slowest one, so a staged call wants
-        // few, fat channels: 128 KiB each (a block moves that in under 3 us)
-        ctas = (int)((bytes + (128u << 10) - 1) / (128u << 10));
+        // few, fat channels: 64 KiB each (a block moves that in about a microsecond)
+        ctas = (int)((bytes + (64u << 10) - 1) / (64u << 10));
         if (ctas > coll_ctas_) ctas = coll_ctas_;
         if (ctas < 1) ctas = 1;
       }

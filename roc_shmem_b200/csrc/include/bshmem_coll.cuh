@@ -120,9 +120,11 @@ __device__ __forceinline__ int team_sync(const State& s, const Team& t, int cta 
   __syncthreads();                       // all stores of the block precede the release below
   uint64_t epoch = *epoch_addr(s, t.slot, cta) + 1;
   if (tid < t.size) {
+    // release pattern: one system fence per signalling thread, then the flag.  The block barrier above makes every
+    // thread's earlier stores (remote ones included) precede this fence, so they are visible to whoever sees the flag.
     asm volatile("fence.acq_rel.sys;" ::: "memory");
     uint64_t* remote = flag_addr(s, dev::team_pe(t, tid), t.slot, cta, t.my_idx);
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(remote), "l"(epoch) : "memory");
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(remote), "l"(epoch) : "memory");
     const uint64_t* mine = flag_addr(s, s.my_pe, t.slot, cta, tid);
     int rc = dev::wait_until<uint64_t>(s, mine, BSHMEM_CMP_GE, epoch, BSHMEM_WHERE_BARRIER, dev::team_pe(t, tid));
     if (rc != BSHMEM_OK) sync_status = rc;
@@ -140,9 +142,10 @@ __device__ __forceinline__ int team_sync(const State& s, const Team& t, int cta 
   __syncthreads();
   return rc;
 }
-// barrier = quiet + sync
+// barrier = quiet + sync.  The sync's own release (block barrier, then a system fence by each signalling thread before
+// its flag store) already orders every earlier store of the calling block, puts to peers included, before the flags;
+// a second fence by all threads of the block would only add system-scope fences that contend across blocks.
 __device__ __forceinline__ int team_barrier(const State& s, const Team& t, int cta = 0) {
-  asm volatile("fence.acq_rel.sys;" ::: "memory");
   return team_sync(s, t, cta);
 }
 __device__ __forceinline__ int wg_barrier_all(const State& s) { return team_barrier(s, dev::team_world(s)); }
@@ -742,6 +745,33 @@ __device__ __forceinline__ int team_reduce_staged(const State& s, const Team& t,
   reduce_range<T>(s, op, t.size, srcs, t.size, dsts, sb + b, sb + e, bulk);
   if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, n * sizeof(T)); }
   return team_barrier(s, t, cta);
+}
+
+// allreduce, ONE exchange: every PE pushes its whole vector into its block of every member's staging, one barrier,
+// then every PE reduces all blocks locally (same order everywhere, so the results are identical).  Moves (size - 1)
+// times the vector per PE instead of 2 (size - 1) / size times, which pays while the second exchange of the two-shot
+// form costs more than the extra bytes (the host picks; the vector must fit a sender's block).  dest may alias source.
+template <typename T>
+__device__ __forceinline__ int team_reduce_staged_oneshot(const State& s, const Team& t, int op, T* dest, const T* source, size_t n,
+                                                          unsigned long long seq, int cta, int ncta, char* bulk = nullptr) {
+  constexpr size_t VE = 16 / sizeof(T);
+  const size_t slot = (BSHMEM_STAGE_BYTES / t.size) & ~(size_t)15;
+  size_t b, e;
+  split_range(n, ncta, cta, VE, &b, &e);
+  for (int k = 1; k < t.size; ++k) {
+    const int j = (t.my_idx + k) % t.size;
+    dev::copy_bytes<dev::BLOCK>(stage_half(s, dev::team_pe(t, j), seq) + (size_t)t.my_idx * slot + b * sizeof(T),
+                                reinterpret_cast<const char*>(source + b), (e - b) * sizeof(T));
+  }
+  int rc = team_barrier(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  const T* srcs[BSHMEM_MAX_PES];
+  const char* st = stage_half(s, s.my_pe, seq);
+  for (int k = 0; k < t.size; ++k) srcs[k] = k == t.my_idx ? source : reinterpret_cast<const T*>(st + (size_t)k * slot);
+  T* mine[1] = {dest};
+  reduce_range<T>(s, op, t.size, srcs, 1, mine, b, e, bulk);
+  if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, n * sizeof(T)); }
+  return BSHMEM_OK;
 }
 
 // ---- NVLink-multicast (NVLS) allreduce: the switch reduces and broadcasts ----------------------
