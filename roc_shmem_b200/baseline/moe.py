@@ -38,9 +38,12 @@ def moe_reference_single(x, wr, w1, w3, w2, topk, compute_dtype=torch.float32, r
 class NcclMoE(torch.nn.Module):
     """Expert-parallel MoE with NCCL all_to_all and cuBLAS, one expert group per rank."""
 
-    def __init__(self, wr, w1, w3, w2, topk: int):
+    def __init__(self, wr, w1, w3, w2, topk: int, router_grad: bool = False):
+        """With `router_grad` the routing weights stay in the autograd graph: backward also yields the router weight
+        gradient and the router's share of the input gradient (what MoELayer.backward computes)."""
         super().__init__()
-        self.wr = wr
+        self.router_grad = router_grad
+        self.wr = torch.nn.Parameter(wr.clone()) if router_grad else wr
         self.w1 = torch.nn.Parameter(w1)      # [G, F, H] local experts
         self.w3 = torch.nn.Parameter(w3)
         self.w2 = torch.nn.Parameter(w2)      # [G, H, F]
@@ -51,7 +54,7 @@ class NcclMoE(torch.nn.Module):
         G = self.w1.shape[0]
         E = G * P
         T, H = x.shape
-        idx, w = route(x.detach(), self.wr, self.topk)
+        idx, w = route(x if self.router_grad else x.detach(), self.wr, self.topk)
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         tok = order // self.topk

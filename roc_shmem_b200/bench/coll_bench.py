@@ -82,7 +82,8 @@ def main() -> None:
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     P = dist.get_world_size()
-    rt = shmem.init("device", device=local, heap_bytes=int(args.max_bytes * 2.5) + (256 << 20),
+    # the heap's allocator hands out power-of-two blocks: source + destination + the runtime's own region
+    rt = shmem.init("device", device=local, heap_bytes=4 * args.max_bytes + (512 << 20),
                     nvls="on" if args.nvls else "off", coll_ctas=args.ctas)
     me = rt.my_pe
     dev = rt.device

@@ -63,7 +63,10 @@ def main() -> None:
         T, H, F = args.tokens, 4096, 14336
     G = E // P
     cap_rows = int(T * topk * P / E * 1.25)
-    heap = 2 * (G * cap_rows * H * 2) + 2 * (T * topk * H * 2) + (512 << 20)
+    # the heap's allocator hands out power-of-two blocks: two receive buffers (forward, backward), two per-entry
+    # return buffers, the runtime's own region and small tables
+    p2 = lambda n: 1 << max(n - 1, 1).bit_length()
+    heap = 2 * p2((G * cap_rows + 256) * H * 2) + 2 * p2(T * topk * H * 2) + (1 << 30)
     rt = shmem.init("device", device=local, heap_bytes=heap, timeout_ms=20000)
     dev = rt.device
     torch.manual_seed(7)                                   # same weights on every rank, sliced per rank
@@ -91,7 +94,7 @@ def main() -> None:
 
     ok = True
     if not args.no_baseline:
-        base = NcclMoE(wr, w1.clone(), w3.clone(), w2.clone(), topk)
+        base = NcclMoE(wr, w1.clone(), w3.clone(), w2.clone(), topk, router_grad=True)   # same work as ours: router backward included
         xb = x.clone().requires_grad_(True)
         yb = base(xb)
         yb.backward(dout)

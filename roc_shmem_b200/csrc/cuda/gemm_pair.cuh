@@ -199,6 +199,13 @@ struct Chunk {
 
 struct PolicyDefaults {
   struct EpiState {};
+  // Gated epilogue: inside every 64-column chunk of the accumulator, columns 0-31 are gate pre-activations and 32-63
+  // the matching up-projections; the epilogue writes silu(gate) * up, i.e. half as many output columns (the two
+  // chunks of a warp make one 32 x 64 output box; out_target gets the OUTPUT column).
+  static constexpr bool kGated = false;
+  // first row of the 256-row block of A / of the 256-row block of B that tile (m_blk, n_blk) multiplies
+  template <class Params> __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * BM; }
+  template <class Params> __device__ static __forceinline__ int b_row(const Params&, int, int n_blk) { return n_blk * BN; }
   template <class Params> __device__ static __forceinline__ bool a_ready(const Params&, int, Guard&) { return true; }
   template <class Params> __device__ static __forceinline__ int num_tiles(const Params& p) {
     return p.core.num_m_blocks * p.core.num_n_blocks;
@@ -222,6 +229,7 @@ struct PolicyDefaults {
 //   tile_coords(prm, tile, &m_blk, &n_blk)     tile = index in the pair's schedule (pair id + k * pairs)
 //   a_ready(prm, m_blk, guard)            producer lane, before a tile's first A load (rows of the whole 256-row block)
 //   out_target(prm, row, col, &map, &x, &y)    where the 32x64 chunk starting at C[row, col] goes (map may be null)
+//   a_row(prm, m_blk), b_row(prm, m_blk, n_blk), kGated                          (defaults in PolicyDefaults)
 //   the hooks of PolicyDefaults
 template <class P>
 __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uint8_t* smem_raw) {
@@ -277,8 +285,8 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         int m_blk, n_blk;
         P::tile_coords(prm, tile, &m_blk, &n_blk);
         if (!P::a_ready(prm, m_blk, g)) break;
-        const int a_row = m_blk * BM + (int)rank * CTA_M;
-        const int b_row = n_blk * BN + (int)rank * CTA_NLOAD;
+        const int a_row = P::a_row(prm, m_blk) + (int)rank * CTA_M;
+        const int b_row = P::b_row(prm, m_blk, n_blk) + (int)rank * CTA_NLOAD;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!pair_wait(L.empty(s), ph ^ 1, g, ERR_PRODUCER_EMPTY)) { ok = false; break; }
 #ifdef BSHMEM_PAIR_TMA2
@@ -356,7 +364,7 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       P::tile_coords(prm, tile, &ck.m_blk, &ck.n_blk);
       ck.ordinal = ord;
       ck.half = (int)rank;
-      ck.row0 = ck.m_blk * BM + (int)rank * CTA_M + quarter * 32;
+      ck.row0 = P::a_row(prm, ck.m_blk) + (int)rank * CTA_M + quarter * 32;
       ck.col0 = ck.n_blk * BN + colhalf * 128;
       // the tensor core is busy with this tile: do useful work until the accumulator is ready
       while (!mbar_try_wait_cluster(L.tmem_full(acc), ((full_ph >> acc) & 1))) {
@@ -369,44 +377,85 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       full_ph ^= 1u << acc;
       ptx::tc_fence_after();
       if (!P::tile_begin(prm, L, st, ck, ew, lane, g)) { ok = false; break; }
+      if constexpr (!P::kGated) {
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[2][32];
-        uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * ACC_COLS + colhalf * 128 + c * EPI_COLS;
-        ptx::tmem_ld_32x32b_x32(taddr, v[0]);
-        ptx::tmem_ld_32x32b_x32(taddr + 32, v[1]);
-        ptx::tmem_ld_wait();
-        if (c == 1) {
-          // all TMEM reads of this warp are done: hand the accumulator back to the MMA issuer
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa(L.tmem_empty(acc), 0));
-        }
-        float f[64];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[2][32];
+          uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * ACC_COLS + colhalf * 128 + c * EPI_COLS;
+          ptx::tmem_ld_32x32b_x32(taddr, v[0]);
+          ptx::tmem_ld_32x32b_x32(taddr + 32, v[1]);
+          ptx::tmem_ld_wait();
+          if (c == 1) {
+            // all TMEM reads of this warp are done: hand the accumulator back to the MMA issuer
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa(L.tmem_empty(acc), 0));
+          }
+          float f[64];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) f[i] = __uint_as_float(v[i >> 5][i & 31]);
-        // the previous chunk's TMA store must have finished reading the staging buffer
-        if (lane == 0) ptx::tma_wait_group_read<0>();
+          for (int i = 0; i < 64; ++i) f[i] = __uint_as_float(v[i >> 5][i & 31]);
+          // the previous chunk's TMA store must have finished reading the staging buffer
+          if (lane == 0) ptx::tma_wait_group_read<0>();
+          __syncwarp();
+          Chunk cc = ck;
+          cc.col0 = ck.col0 + c * EPI_COLS;
+          P::adjust(prm, L, st, cc, f, ew, lane);
+          // row = lane; 8 x 16-byte pieces, piece j lives at (j ^ (row & 7)) under the 128-byte swizzle
+          const uint32_t rowbase = L.epi(ew) + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t w0 = pack_bf16(f[j * 8 + 0], f[j * 8 + 1]);
+            uint32_t w1 = pack_bf16(f[j * 8 + 2], f[j * 8 + 3]);
+            uint32_t w2 = pack_bf16(f[j * 8 + 4], f[j * 8 + 5]);
+            uint32_t w3 = pack_bf16(f[j * 8 + 6], f[j * 8 + 7]);
+            uint32_t dst = rowbase + ((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const CUtensorMap* map; int x, y;
+            P::out_target(prm, cc.row0, cc.col0, &map, &x, &y);
+            if (map != nullptr) ptx::tma_store_2d(map, L.epi(ew), x, y);
+            ptx::tma_commit_group();
+          }
+        }
+      } else {
+        // the warp's two 64-column chunks (32 gate + 32 up each) make one 64-column output chunk
+        if (lane == 0) ptx::tma_wait_group_read<0>();     // the previous tile's store has read the staging buffer
         __syncwarp();
-        Chunk cc = ck;
-        cc.col0 = ck.col0 + c * EPI_COLS;
-        P::adjust(prm, L, st, cc, f, ew, lane);
-        // row = lane; 8 x 16-byte pieces, piece j lives at (j ^ (row & 7)) under the 128-byte swizzle
         const uint32_t rowbase = L.epi(ew) + lane * 128;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint32_t w0 = pack_bf16(f[j * 8 + 0], f[j * 8 + 1]);
-          uint32_t w1 = pack_bf16(f[j * 8 + 2], f[j * 8 + 3]);
-          uint32_t w2 = pack_bf16(f[j * 8 + 4], f[j * 8 + 5]);
-          uint32_t w3 = pack_bf16(f[j * 8 + 6], f[j * 8 + 7]);
-          uint32_t dst = rowbase + ((j ^ (lane & 7)) << 4);
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        for (int hc = 0; hc < 2; ++hc) {
+          uint32_t v[2][32];
+          uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * ACC_COLS + colhalf * 128 + hc * EPI_COLS;
+          ptx::tmem_ld_32x32b_x32(taddr, v[0]);        // gate
+          ptx::tmem_ld_32x32b_x32(taddr + 32, v[1]);   // up
+          ptx::tmem_ld_wait();
+          if (hc == 1) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa(L.tmem_empty(acc), 0));
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float g0 = __uint_as_float(v[0][j * 8 + 2 * q]), g1 = __uint_as_float(v[0][j * 8 + 2 * q + 1]);
+              float u0 = __uint_as_float(v[1][j * 8 + 2 * q]), u1 = __uint_as_float(v[1][j * 8 + 2 * q + 1]);
+              float h0 = g0 / (1.f + __expf(-g0)) * u0, h1 = g1 / (1.f + __expf(-g1)) * u1;
+              w[q] = pack_bf16(h0, h1);
+            }
+            uint32_t dst = rowbase + (((hc * 4 + j) ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+          }
         }
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
           const CUtensorMap* map; int x, y;
-          P::out_target(prm, cc.row0, cc.col0, &map, &x, &y);
+          P::out_target(prm, ck.row0, ck.col0 / 2, &map, &x, &y);     // output column = half the accumulator column
           if (map != nullptr) ptx::tma_store_2d(map, L.epi(ew), x, y);
           ptx::tma_commit_group();
         }

@@ -448,8 +448,11 @@ class GpuBackend final : public Backend {
           if (bytes <= slot && bytes * (P - 1) * (P - 2) / P <= (5ull << 20)) a.stage_oneshot = 1;
         }
         // every channel runs its own flag exchange and the kernel ends with the slowest one, so a staged call wants
-        // few, fat channels: 64 KiB each (a block moves that in about a microsecond)
-        ctas = (int)((bytes + (64u << 10) - 1) / (64u << 10));
+        // few, fat channels; a block pushes its share to P-1 peers at about 50 GB/s, so the share shrinks with P:
+        // 64 KiB with two PEs, 32 KiB with four, 16 KiB with eight and more
+        uint64_t gran = (128ull << 10) / (uint64_t)heap_->n_pes;
+        if (gran < (16u << 10)) gran = 16u << 10;
+        ctas = (int)((bytes + gran - 1) / gran);
         if (ctas > coll_ctas_) ctas = coll_ctas_;
         if (ctas < 1) ctas = 1;
       }

@@ -1,5 +1,7 @@
-// moe_gemm.cu — grouped (per-expert) tcgen05 GEMM for the MoE layer, built on the
-// persistent main loop of gemm_core.cuh.
+// moe_gemm.cu — grouped (per-expert) tcgen05 GEMM for the MoE layer.  The K-major forms (gate/up, down and the two
+// data-gradient GEMMs) run on the CTA-pair main loop of gemm_pair.cuh (cta_group::2, the epilogue of one tile overlaps
+// the MMAs of the next); the weight-gradient form on token-major operands and the ragged-K form run on the
+// single-CTA main loop of gemm_core.cuh.
 //
 //   C_g = A_g · B_g^T  for every local expert g, all operands K-major bf16:
 //     rows mode   A: [G][cap rows][K]   B: [G][N][K]    C: [G][cap][N]
@@ -14,7 +16,7 @@
 // moe_kernels.cu.
 #include <cstdlib>
 
-#include "gemm_core.cuh"
+#include "gemm_pair.cuh"
 #include "moe_common.h"
 #include "tma_host.h"
 
@@ -145,6 +147,52 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) grouped_gemm_tn_kernel(const _
   gemm_mainloop<GroupedTN>(prm, smem_raw);
 }
 
+// ---- the K-major rows mode on CTA pairs ---------------------------------------------------------------------------
+// Same tile schedule (a tile is 256 rows of one group x 256 accumulator columns) and the same parameters; each CTA of
+// the pair loads 128 rows of the A block and 128 rows of the B block, so the tensor maps have 128-row boxes.
+namespace g2 = bshmem::gemm2;
+
+template <bool kGatedEpi>
+struct GroupedPair : g2::PolicyDefaults {
+  using Params = GroupedParams;
+  using Base = Grouped<kGatedEpi>;
+  static constexpr bool kGated = kGatedEpi;
+  __device__ static __forceinline__ const CoreParams& core(const Params& p) { return p.core; }
+  __device__ static __forceinline__ const CUtensorMap* map_a(const Params& p) { return &p.map_a; }
+  __device__ static __forceinline__ const CUtensorMap* map_b(const Params& p) { return &p.map_b; }
+  __device__ static __forceinline__ int num_tiles(const Params& p) { return Base::num_tiles(p); }
+  __device__ static __forceinline__ void tile_coords(const Params& p, int tile, int* m_blk, int* n_blk) {
+    Base::tile_coords(p, tile, m_blk, n_blk);
+  }
+  __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * g2::BM; }
+  __device__ static __forceinline__ int b_row(const Params& p, int m_blk, int n_blk) {
+    return (m_blk / p.a_blocks_per_group) * p.b_rows_per_group + n_blk * g2::BN;
+  }
+  // runs in the producer lane of BOTH CTAs: each loads its own half of the block
+  __device__ static __forceinline__ bool a_ready(const Params& p, int, Guard& g) {
+    for (int s = 0; s < p.P; ++s)
+      if (!wait_ge<true>(p.arrive + s, (unsigned long long)p.expected[s], g, g2::ERR_PEER_SIGNAL)) return false;
+    if (p.P) ptx::fence_proxy_async_all();   // peer stores (generic proxy) before the TMA reads
+    return true;
+  }
+  __device__ static __forceinline__ void out_target(const Params& p, int row, int col, const CUtensorMap** map, int* x, int* y) {
+    *map = &p.map_c;       // rows beyond a group's count are scratch inside the group's own region
+    *x = col;
+    *y = row;
+  }
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g2::NUM_THREADS, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ GroupedParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  g2::gemm_mainloop<GroupedPair<false>>(prm, smem_raw);
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g2::NUM_THREADS, 1)
+grouped_gemm_pair_gated_kernel(const __grid_constant__ GroupedParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  g2::gemm_mainloop<GroupedPair<true>>(prm, smem_raw);
+}
+
 // Zero the token rows [count_g, next multiple of 64) — rows [0, 64) of an empty group — of every group of a
 // [G][cap][cols] bf16 buffer.
 __global__ void zero_pad_rows_kernel(__nv_bfloat16* buf, const int* counts, int cap, int cols) {
@@ -161,6 +209,7 @@ __global__ void zero_pad_rows_kernel(__nv_bfloat16* buf, const int* counts, int 
 
 int* g_err_dev[64] = {};
 int g_sms[64] = {};
+int g_pairs[64] = {};
 
 int ensure(int dev) {
   if (g_err_dev[dev]) return 0;
@@ -170,6 +219,9 @@ int ensure(int dev) {
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_gated_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g2::SMEM_BYTES));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_pair_gated_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g2::SMEM_BYTES));
+  g_pairs[dev] = g2::max_resident_pairs(grouped_gemm_pair_kernel, g_sms[dev]);
   return 0;
 }
 
@@ -207,16 +259,28 @@ int bshmem_moe_grouped_gemm(const void* A, const void* B, void* C, int G, int a_
   p.b_rows_per_group = b_rows_per_group;
   p.group_m = 16;
   p.P = P; p.arrive = static_cast<const unsigned long long*>(arrive); p.expected = expected;
-  rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)G * a_rows_per_group, K, lda, BM, 64);
+  // K-major rows mode with a uniform reduction length: CTA pairs; a ragged reduction length (legacy weight-gradient
+  // form on transposed copies) stays on the single-CTA loop
+  const bool pair = klen_dev == nullptr && g_pairs[dev] > 0;
+  const int box_rows_a = pair ? g2::CTA_M : BM, box_rows_b = pair ? g2::CTA_NLOAD : BN;
+  rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)G * a_rows_per_group, K, lda, box_rows_a, 64);
   if (rc) return rc;
-  rc = host::make_tmap_2d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, (uint64_t)G * b_rows_per_group, K, ldb, BN, 64);
+  rc = host::make_tmap_2d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, (uint64_t)G * b_rows_per_group, K, ldb, box_rows_b, 64);
   if (rc) return rc;
   rc = host::make_tmap_2d(&p.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, (uint64_t)G * a_rows_per_group, gated ? N / 2 : N, ldc, 32, EPI_COLS);
   if (rc) return rc;
-  int ctas = g_sms[dev];
-  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  if (gated) grouped_gemm_gated_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
-  else grouped_gemm_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pair) {
+    int pairs = g_pairs[dev];
+    if (max_ctas > 1 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
+    if (gated) grouped_gemm_pair_gated_kernel<<<2 * pairs, g2::NUM_THREADS, g2::SMEM_BYTES, st>>>(p);
+    else grouped_gemm_pair_kernel<<<2 * pairs, g2::NUM_THREADS, g2::SMEM_BYTES, st>>>(p);
+  } else {
+    int ctas = g_sms[dev];
+    if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+    if (gated) grouped_gemm_gated_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, st>>>(p);
+    else grouped_gemm_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, st>>>(p);
+  }
   BSHMEM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

@@ -104,3 +104,31 @@ def test_gemm_reduce_scatter_fp8_single_pe_equals_plain_kernel():
         op.close()
     finally:
         shmem.finalize()
+
+
+def test_gemm_reduce_scatter_fp8_one_k_block_per_tile():
+    """K = 128 is a single k-block, so a tile is finished as soon as it is started and the epilogue warps of a block
+    run several tiles apart: the per-tile publish counters (four, indexed by tile ordinal) must not mix tiles.
+    512 tiles of 128 x 256 on 148 blocks; checked against the plain kernel (bit for bit) and a float32 reference."""
+    import roc_shmem_b200 as shmem
+    from roc_shmem_b200.ops.gemm_fp8 import GemmReduceScatterFp8, gemm_fp8, quantize_act, quantize_weight
+    rt = shmem.init("device", rank=0, world_size=1, heap_bytes=512 << 20, timeout_ms=5000)
+    try:
+        torch.manual_seed(16)
+        M, N, K = 8192, 2048, 128
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+        qa, qw = quantize_act(x), quantize_weight(w)
+        op = GemmReduceScatterFp8(rt, M, N, K)
+        ref = gemm_fp8(qa, qw)
+        full = x.float() @ w.float().t()
+        for _ in range(3):
+            op.out.fill_(7.0)
+            op(qa, qw)
+            torch.cuda.synchronize()
+            op.check()
+            assert torch.equal(op.out, ref)
+        assert (op.out.float() - full).abs().max().item() <= 0.06 * full.abs().max().item()
+        op.close()
+    finally:
+        shmem.finalize()
