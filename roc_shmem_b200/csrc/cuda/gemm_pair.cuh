@@ -106,17 +106,6 @@ __device__ __forceinline__ void umma2_f16(uint32_t d_tmem, uint64_t a_desc, uint
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-#ifdef BSHMEM_PAIR_TMA2
-// Tiled load of this CTA's own shared memory whose completion bytes are counted on a barrier of the pair's FIRST
-// CTA (the cta_group::2 form allows the barrier to live in either CTA of the pair).  Not a multicast load: one
-// CTA, one destination.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* m, uint32_t cluster_bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(x), "r"(y)
-      : "memory");
-}
-#endif
 // One commit that arrives on the barrier at this offset in BOTH CTAs of the pair (two single-destination commits
 // per k-block cost the issuing thread 6 % of the GEMM's throughput).
 __device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
@@ -203,6 +192,22 @@ struct PolicyDefaults {
   // the matching up-projections; the epilogue writes silu(gate) * up, i.e. half as many output columns (the two
   // chunks of a warp make one 32 x 64 output box; out_target gets the OUTPUT column).
   static constexpr bool kGated = false;
+  // Operand layout.  Default: both operands K-major, one 128-row x 128-byte TMA box per operand, CTA and stage, and
+  // shared-memory descriptors that step 32 bytes along K inside the swizzle atom.  A policy with MN-major operands
+  // overrides the instruction descriptor, the stage-0 descriptors, the step per MMA and the loads.
+  static constexpr uint32_t kIdesc = kIdescBf16;
+  static constexpr uint32_t kKStepBytes = UMMA_K_BYTES;
+  __device__ static __forceinline__ uint64_t desc_a0(uint32_t a0) { return ptx::umma_desc_sw128(a0); }
+  __device__ static __forceinline__ uint64_t desc_b0(uint32_t b0) { return ptx::umma_desc_sw128(b0); }
+  // a_row / b_row: first row this CTA loads (its rank's half included); kb: k-block of the tile
+  template <class Params>
+  __device__ static __forceinline__ void load_stage(const Params&, const CUtensorMap* ma, const CUtensorMap* mb, uint32_t a_smem,
+                                                    uint32_t b_smem, uint32_t bar, int kb, int a_row, int b_row, int, int, int) {
+    ptx::tma_load_2d(a_smem, ma, bar, kb * BK, a_row);
+    ptx::tma_load_2d(b_smem, mb, bar, kb * BK, b_row);
+  }
+  // k-blocks of the tile's reduction (ragged per group in the grouped weight-gradient GEMM); at least 1
+  template <class Params> __device__ static __forceinline__ int num_kb(const Params& p, int) { return (p.core.K + BK - 1) / BK; }
   // first row of the 256-row block of A / of the 256-row block of B that tile (m_blk, n_blk) multiplies
   template <class Params> __device__ static __forceinline__ int a_row(const Params&, int m_blk) { return m_blk * BM; }
   template <class Params> __device__ static __forceinline__ int b_row(const Params&, int, int n_blk) { return n_blk * BN; }
@@ -240,7 +245,6 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
   const uint32_t rank = cluster_ctarank();            // 0 issues the MMAs
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int num_tiles = P::num_tiles(prm);
-  const int num_kb = (cp.K + BK - 1) / BK;
   Guard g{cp.err, L.abort_flag(), cp.timeout_ns};
 
   if (threadIdx.x == 0) {
@@ -249,11 +253,7 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
     for (int i = 0; i < 8; ++i) L.scratch()[i] = 0;
     for (int s = 0; s < STAGES; ++s) {
       // first CTA: its own producer's expect_tx arrival plus the relay's arrival for the second CTA's stage
-#ifdef BSHMEM_PAIR_TMA2
-      ptx::mbar_init(L.full(s), 1);
-#else
       ptx::mbar_init(L.full(s), rank == 0 ? 2 : 1);
-#endif
       ptx::mbar_init(L.empty(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -285,20 +285,13 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         int m_blk, n_blk;
         P::tile_coords(prm, tile, &m_blk, &n_blk);
         if (!P::a_ready(prm, m_blk, g)) break;
+        const int num_kb = P::num_kb(prm, m_blk);
         const int a_row = P::a_row(prm, m_blk) + (int)rank * CTA_M;
         const int b_row = P::b_row(prm, m_blk, n_blk) + (int)rank * CTA_NLOAD;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!pair_wait(L.empty(s), ph ^ 1, g, ERR_PRODUCER_EMPTY)) { ok = false; break; }
-#ifdef BSHMEM_PAIR_TMA2
-          if (rank == 0) ptx::mbar_arrive_expect_tx(L.full(s), 2 * STAGE_BYTES);
-          const uint32_t fb = mapa(L.full(s), 0);
-          tma_load_2d_pair(L.a(s), P::map_a(prm), fb, kb * BK, a_row);
-          tma_load_2d_pair(L.b(s), P::map_b(prm), fb, kb * BK, b_row);
-#else
           ptx::mbar_arrive_expect_tx(L.full(s), STAGE_BYTES);
-          ptx::tma_load_2d(L.a(s), P::map_a(prm), L.full(s), kb * BK, a_row);
-          ptx::tma_load_2d(L.b(s), P::map_b(prm), L.full(s), kb * BK, b_row);
-#endif
+          P::load_stage(prm, P::map_a(prm), P::map_b(prm), L.a(s), L.b(s), L.full(s), kb, a_row, b_row, m_blk, n_blk, (int)rank);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -310,9 +303,12 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
       uint32_t acc_ph = 0;          // bit a = phase of accumulator a
       int ord = 0;
       bool ok = true;
-      const uint64_t desc_a0 = ptx::umma_desc_sw128(L.a(0)), desc_b0 = ptx::umma_desc_sw128(L.b(0));
+      const uint64_t desc_a0 = P::desc_a0(L.a(0)), desc_b0 = P::desc_b0(L.b(0));
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++ord) {
         const int acc = ord & 1;
+        int m_blk, n_blk;
+        P::tile_coords(prm, tile, &m_blk, &n_blk);
+        const int num_kb = P::num_kb(prm, m_blk);
         // the epilogue warps of both CTAs must have drained this accumulator (two tiles ago)
         if (!pair_wait(L.tmem_empty(acc), ((acc_ph >> acc) & 1) ^ 1, g, ERR_MMA_TMEM_EMPTY)) break;
         acc_ph ^= 1u << acc;
@@ -326,7 +322,7 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
           const uint64_t db = desc_b0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < BK_BYTES / UMMA_K_BYTES; ++k)
-            umma2_f16(d_tmem, da + (uint64_t)((k * UMMA_K_BYTES) >> 4), db + (uint64_t)((k * UMMA_K_BYTES) >> 4), kIdescBf16,
+            umma2_f16(d_tmem, da + (uint64_t)((k * P::kKStepBytes) >> 4), db + (uint64_t)((k * P::kKStepBytes) >> 4), P::kIdesc,
                       (kb | k) != 0 ? 1u : 0u);
           umma2_commit_both(L.empty(s));       // stage reusable in both CTAs once these MMAs retire
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -335,12 +331,14 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         umma2_commit_both(L.tmem_full(acc));
       }
     }
-#ifndef BSHMEM_PAIR_TMA2
     else if (lane == 0) {
       // ------------------------------ relay (second CTA) --------------------------------------
       int s = 0; uint32_t ph = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int m_blk, n_blk;
+        P::tile_coords(prm, tile, &m_blk, &n_blk);
+        const int num_kb = P::num_kb(prm, m_blk);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!pair_wait(L.full(s), ph, g, ERR_RELAY_FULL)) { ok = false; break; }
           mbar_arrive_cluster(mapa(L.full(s), 0));
@@ -348,7 +346,6 @@ __device__ __forceinline__ void gemm_mainloop(const typename P::Params& prm, uin
         }
       }
     }
-#endif
   } else {
     // ------------------------------ epilogue (both CTAs) ------------------------------------
     const int ew = warp - 2;               // 0..7

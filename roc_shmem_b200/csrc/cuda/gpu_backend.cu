@@ -418,7 +418,7 @@ class GpuBackend final : public Backend {
       // those under which the kernel takes that path, and every PE makes the same sequence of such calls, so this
       // counter is the same everywhere and its parity alternates between consecutive uses of the slots.
       a.ll_epoch = ++ll_epoch_;
-      ctas = (int)((bytes + (8u << 10) - 1) / (8u << 10));      // 8 KiB of payload per block
+      ctas = (int)((bytes + (4u << 10) - 1) / (4u << 10));      // 4 KiB of payload per block: four words per thread, polled one after the other
       if (ctas > coll_ctas_) ctas = coll_ctas_;
     }
     // One exchange through the staging region instead of sync + work + barrier: world team, what a PE receives fits a

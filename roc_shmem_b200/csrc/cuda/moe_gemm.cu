@@ -182,6 +182,38 @@ struct GroupedPair : g2::PolicyDefaults {
   }
 };
 
+// Weight-gradient flavour on CTA pairs: both operands MN-major (token-major activations as they are), ragged
+// reduction over the group's tokens.  Per CTA and stage, each operand is two 64-wide MN blocks of 64 tokens (8 KiB per
+// block, 128-byte swizzle), i.e. the CTA's 128 of the tile's 256 rows / columns.
+struct GroupedPairTN : GroupedPair<false> {
+  static constexpr uint32_t kIdesc = ptx::umma_idesc_mn_major(1, 1, g2::BM, g2::BN);
+  static constexpr uint32_t kBlock = 64 * g2::BK_BYTES;         // one 64 (MN) x 64 (tokens) block: 8 KiB
+  static constexpr uint32_t kKStepBytes = 2048;                 // one MMA consumes 16 tokens = two swizzle atoms
+  __device__ static __forceinline__ uint64_t desc_a0(uint32_t a0) { return ptx::umma_desc_sw128_ex(a0, kBlock, 1024); }
+  __device__ static __forceinline__ uint64_t desc_b0(uint32_t b0) { return ptx::umma_desc_sw128_ex(b0, kBlock, 1024); }
+  __device__ static __forceinline__ int num_kb(const Params& p, int m_blk) {
+    const int n = (p.klen[m_blk / p.a_blocks_per_group] + 63) / 64;
+    return n < 1 ? 1 : n;     // an empty group still runs one (all-zero) k-block so that C becomes 0
+  }
+  __device__ static __forceinline__ bool a_ready(const Params&, int, Guard&) { return true; }
+  __device__ static __forceinline__ void load_stage(const Params& p, const CUtensorMap* ma, const CUtensorMap* mb, uint32_t a_smem,
+                                                    uint32_t b_smem, uint32_t bar, int kb, int, int, int m_blk, int n_blk, int rank) {
+    const int g = m_blk / p.a_blocks_per_group;
+    const int tok = g * p.k_rows_per_group + kb * 64;
+    const int m0 = (m_blk - g * p.a_blocks_per_group) * g2::BM + rank * g2::CTA_M, n0 = n_blk * g2::BN + rank * g2::CTA_NLOAD;
+    if (p.tn3d) {                  // one 16 KiB copy per operand: {64, 64 tokens, 2 column blocks}
+      ptx::tma_load_3d(a_smem, ma, bar, 0, tok, m0 / 64);
+      ptx::tma_load_3d(b_smem, mb, bar, 0, tok, n0 / 64);
+      return;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      ptx::tma_load_2d(a_smem + i * kBlock, ma, bar, m0 + i * 64, tok);
+      ptx::tma_load_2d(b_smem + i * kBlock, mb, bar, n0 + i * 64, tok);
+    }
+  }
+};
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g2::NUM_THREADS, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ GroupedParams prm) {
   extern __shared__ uint8_t smem_raw[];
@@ -191,6 +223,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g2::NUM_THREADS, 1)
 grouped_gemm_pair_gated_kernel(const __grid_constant__ GroupedParams prm) {
   extern __shared__ uint8_t smem_raw[];
   g2::gemm_mainloop<GroupedPair<true>>(prm, smem_raw);
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g2::NUM_THREADS, 1)
+grouped_gemm_pair_tn_kernel(const __grid_constant__ GroupedParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  g2::gemm_mainloop<GroupedPairTN>(prm, smem_raw);
 }
 
 // Zero the token rows [count_g, next multiple of 64) — rows [0, 64) of an empty group — of every group of a
@@ -221,6 +258,7 @@ int ensure(int dev) {
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g2::SMEM_BYTES));
   BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_pair_gated_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g2::SMEM_BYTES));
+  BSHMEM_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_pair_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g2::SMEM_BYTES));
   g_pairs[dev] = g2::max_resident_pairs(grouped_gemm_pair_kernel, g_sms[dev]);
   return 0;
 }
@@ -309,12 +347,17 @@ int bshmem_moe_grouped_gemm_tn(const void* A, const void* B, void* C, int G, int
   p.a_blocks_per_group = M / BM;
   p.k_rows_per_group = cap;
   p.group_m = 16;
+  // CTA pairs unless the single-CTA loop is asked for (B200SHMEM_TN_SINGLE, kept for comparison): a CTA then loads
+  // two 64-wide column blocks per operand and stage instead of four
+  static const bool single = getenv("B200SHMEM_TN_SINGLE") != nullptr;
+  const bool pair = !single && g_pairs[dev] > 0;
+  const uint32_t blocks = pair ? 2 : 4;
   // preferred: one 3-D copy per operand and stage; if the driver refuses that view, boxes of 64 MN-elements
-  // (128 bytes, the swizzle span) by 64 tokens, four per operand and stage
+  // (128 bytes, the swizzle span) by 64 tokens, one per column block
   static const bool no3d = getenv("B200SHMEM_TN_2D") != nullptr;
   p.tn3d = 0;
-  if (!no3d && host::make_tmap_colblocks_3d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, (uint64_t)G * cap, M, lda, 64, 4) == 0 &&
-      host::make_tmap_colblocks_3d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, (uint64_t)G * cap, N, ldb, 64, 4) == 0)
+  if (!no3d && host::make_tmap_colblocks_3d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, (uint64_t)G * cap, M, lda, 64, blocks) == 0 &&
+      host::make_tmap_colblocks_3d(&p.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, (uint64_t)G * cap, N, ldb, 64, blocks) == 0)
     p.tn3d = 1;
   if (!p.tn3d) {
     rc = host::make_tmap_2d(&p.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)G * cap, M, lda, 64, 64);
@@ -324,9 +367,16 @@ int bshmem_moe_grouped_gemm_tn(const void* A, const void* B, void* C, int G, int
   }
   rc = host::make_tmap_2d(&p.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, (uint64_t)G * M, N, ldc, 32, EPI_COLS);
   if (rc) return rc;
-  int ctas = g_sms[dev];
-  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  grouped_gemm_tn_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pair) {
+    int pairs = g_pairs[dev];
+    if (max_ctas > 1 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
+    grouped_gemm_pair_tn_kernel<<<2 * pairs, g2::NUM_THREADS, g2::SMEM_BYTES, st>>>(p);
+  } else {
+    int ctas = g_sms[dev];
+    if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+    grouped_gemm_tn_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, st>>>(p);
+  }
   BSHMEM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

@@ -470,30 +470,44 @@ __device__ __forceinline__ int team_reduce_ll(const State& s, const Team& t, int
   }
   // ---- receive + reduce: unit u = kWords consecutive words of every sender ----
   const unsigned long long t0 = dev::timer();
+  constexpr int kBatch = 8;      // senders polled together: their loads are in flight at the same time
   for (int u = u_begin + threadIdx.x; u < u_end; u += blockDim.x) {
     A acc[kElems];
-    for (int k = 0; k < t.size; ++k) {
-      const char* slot = my_base + slot0 + (size_t)k * slot_bytes + (size_t)u * kWords * 8;
-      uint32_t raw[kWords];
+    for (int k0 = 0; k0 < t.size; k0 += kBatch) {
+      unsigned long long v[kBatch][kWords];
+      const char* slot[kBatch];
 #pragma unroll
-      for (int w = 0; w < kWords; ++w) {
-        unsigned long long v;
-        unsigned it = 0;
-        while (true) {
-          asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(slot + w * 8) : "memory");
-          if ((v >> 32) == (e & 0xFFFFFFFFull)) break;
-          if ((++it & 63) == 0 && dev::timer() - t0 > s.timeout_ns) {
-            dev::record_error(s, BSHMEM_ERR_TIMEOUT, dev::team_pe(t, k), BSHMEM_WHERE_BARRIER, (uint64_t)slot, e, v >> 32);
-            ll_status = BSHMEM_ERR_TIMEOUT;
-            break;
-          }
-        }
-        raw[w] = (uint32_t)v;
+      for (int kk = 0; kk < kBatch; ++kk) {
+        // senders beyond the team re-read the last one (keeps the batch branch-free; the value is not used)
+        const int k = k0 + kk < t.size ? k0 + kk : t.size - 1;
+        slot[kk] = my_base + slot0 + (size_t)k * slot_bytes + (size_t)u * kWords * 8;
+#pragma unroll
+        for (int w = 0; w < kWords; ++w)
+          asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v[kk][w]) : "l"(slot[kk] + w * 8) : "memory");
       }
-      T vals[kElems];
-      memcpy(vals, raw, kUnit);
 #pragma unroll
-      for (int i = 0; i < kElems; ++i) acc[i] = k == 0 ? to_acc<T>(vals[i]) : apply<A>(op, acc[i], to_acc<T>(vals[i]));
+      for (int kk = 0; kk < kBatch; ++kk) {
+        if (k0 + kk >= t.size) break;
+        uint32_t raw[kWords];
+#pragma unroll
+        for (int w = 0; w < kWords; ++w) {
+          unsigned it = 0;
+          while ((v[kk][w] >> 32) != (e & 0xFFFFFFFFull)) {          // not there yet: poll this word alone
+            if ((++it & 63) == 0 && dev::timer() - t0 > s.timeout_ns) {
+              dev::record_error(s, BSHMEM_ERR_TIMEOUT, dev::team_pe(t, k0 + kk), BSHMEM_WHERE_BARRIER, (uint64_t)slot[kk], e, v[kk][w] >> 32);
+              ll_status = BSHMEM_ERR_TIMEOUT;
+              break;
+            }
+            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v[kk][w]) : "l"(slot[kk] + w * 8) : "memory");
+          }
+          raw[w] = (uint32_t)v[kk][w];
+        }
+        T vals[kElems];
+        memcpy(vals, raw, kUnit);
+#pragma unroll
+        for (int i = 0; i < kElems; ++i)
+          acc[i] = (k0 + kk) == 0 ? to_acc<T>(vals[i]) : apply<A>(op, acc[i], to_acc<T>(vals[i]));
+      }
     }
     T out[kElems];
 #pragma unroll

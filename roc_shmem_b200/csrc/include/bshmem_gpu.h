@@ -65,6 +65,10 @@ int bshmem_gpu_api_selftest(bshmem_handle_t h, void* sym_i, void* sym_u, void* s
 int bshmem_gpu_api_matrix(bshmem_handle_t h, void* ring_dev, int team_slot, void* sym_i, void* sym_u, void* sym_f, void* data_sym,
                           void* local_dev, void* coll_sym, int nbytes, int peer, int* results_dev);
 int bshmem_gpu_wg_collectives(bshmem_handle_t h, void* dst_sym, void* src_sym, int n, int* status_out);
+/* One launch of the functional test driver's kernel for test `type` (numbers as in roc_shmem_b200/bench/functional.py). */
+int bshmem_gpu_functional_run(bshmem_handle_t h, int type, int team_slot, int peer, int wgs, int wg_size, int loops, int skip,
+                              uint64_t size, void* sym_a, void* sym_b, void* local_dev, void* words, void* timers_dev, int* status_dev,
+                              long ctx_options, int initiator, unsigned n_bins, float* kernel_ms);
 int bshmem_gpu_set_coll_ctas(bshmem_handle_t h, int n);
 int bshmem_gpu_set_nvls(bshmem_handle_t h, int on);
 int bshmem_gpu_get_state(bshmem_handle_t h, bshmem_dev_state_t* out);
