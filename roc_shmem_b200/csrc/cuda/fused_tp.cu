@@ -62,22 +62,28 @@ struct GemmRs : PolicyDefaults {
   // First every tile whose rows another PE owns: in sub-round s every rank visits the owners me+1, me+2, ...,
   // me-1 and computes row-block s of each, so the P ranks always send to P different owners.  Then the tiles of
   // this PE's own rows, whose epilogue adds the P-1 partials that arrived meanwhile and writes the result.
+  // Tile order.  First the tiles of rows that other PEs own, then this PE's own rows.  Row blocks are taken in groups
+  // of up to kGroupM; inside a group the owner changes slowest (step s: every rank sends to owner me+1+s, so the P
+  // ranks always send to P different owners), then the column block, and the row block of the group fastest: the CTA
+  // pairs that run side by side share a few A row blocks and a few B column blocks, which keeps both in L2.
+  static constexpr int kGroupM = 8;
   __device__ static __forceinline__ void tile_coords(const Params& p, int tile, int* m_blk, int* n_blk) {
     const int num_n = p.core.num_n_blocks;
-    const int send_tiles = (p.P - 1) * p.blocks_per_owner * num_n;
-    if (tile < send_tiles) {
-      int per_sub = (p.P - 1) * num_n;
-      int sub = tile / per_sub, rem = tile - sub * per_sub;
-      int step = rem / num_n;
-      *n_blk = rem - step * num_n;
-      int owner = (p.my_rank + 1 + step) % p.P;
-      *m_blk = owner * p.blocks_per_owner + sub;
-    } else {
-      int t = tile - send_tiles;
-      int sub = t / num_n;
-      *n_blk = t - sub * num_n;
-      *m_blk = p.my_rank * p.blocks_per_owner + sub;
-    }
+    const int bpo = p.blocks_per_owner;
+    const int send_tiles = (p.P - 1) * bpo * num_n;
+    int t = tile, owners = p.P - 1;
+    const bool own = tile >= send_tiles;
+    if (own) { t = tile - send_tiles; owners = 1; }
+    const int per_group = owners * kGroupM * num_n;          // only the last group can be smaller
+    const int sg = t / per_group;
+    const int first = sg * kGroupM;
+    const int rows = min(kGroupM, bpo - first);
+    const int rem = t - sg * per_group;
+    const int per_step = rows * num_n;
+    const int step = rem / per_step, r2 = rem - step * per_step;
+    *n_blk = r2 / rows;
+    const int owner = own ? p.my_rank : (p.my_rank + 1 + step) % p.P;
+    *m_blk = owner * bpo + first + r2 % rows;
   }
   __device__ static __forceinline__ void out_target(const Params& p, int row, int col, const CUtensorMap** map, int* x, int* y) {
     int owner = row / p.rows_per_owner;
