@@ -122,6 +122,7 @@ def declare_runtime_api(lib: C.CDLL) -> None:
     f("bshmem_team_broadcast", _I, _VP, C.c_int32, _VP, _VP, _SZ, _I)
     f("bshmem_team_reduce", _I, _VP, C.c_int32, _I, _I, _VP, _VP, _SZ)
     f("bshmem_team_reduce_scatter", _I, _VP, C.c_int32, _I, _I, _VP, _VP, _SZ)
+    f("bshmem_team_reduce_root", _I, _VP, C.c_int32, _I, _I, _VP, _VP, _SZ, _I)
     f("bshmem_team_fcollect", _I, _VP, C.c_int32, _VP, _VP, _SZ)
     f("bshmem_team_alltoall", _I, _VP, C.c_int32, _VP, _VP, _SZ)
     f("bshmem_barrier", _I, _VP, _I, _I, _I, _VP)

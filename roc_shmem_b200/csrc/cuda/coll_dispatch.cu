@@ -7,7 +7,7 @@ namespace collk {
 namespace {
 enum Unit { U_MOVE, U_F32, U_F16, U_I32, U_I8, U_NONE };
 Unit unit_of(const CollArgs& a) {
-  if (a.kind != BSHMEM_COLL_REDUCE && a.kind != BSHMEM_COLL_REDUCE_SCATTER) return U_MOVE;
+  if (a.kind != BSHMEM_COLL_REDUCE && a.kind != BSHMEM_COLL_REDUCE_SCATTER && a.kind != BSHMEM_COLL_REDUCE_ROOT) return U_MOVE;
   switch (a.dtype) {
     case BSHMEM_FLOAT: case BSHMEM_DOUBLE: return U_F32;
     case BSHMEM_BF16: case BSHMEM_FP16: return U_F16;

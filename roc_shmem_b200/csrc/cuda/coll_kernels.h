@@ -40,6 +40,7 @@ inline void extent(int kind, int dtype, uint64_t count, int team_size, uint64_t*
   const uint64_t es = bshmem_dtype_size(dtype);
   switch (kind) {
     case 3 /* BSHMEM_COLL_REDUCE */: *src_bytes = *dst_bytes = count * es; break;
+    case 8 /* BSHMEM_COLL_REDUCE_ROOT */: *src_bytes = *dst_bytes = count * es; break;
     case 4 /* BSHMEM_COLL_REDUCE_SCATTER */: *src_bytes = count * es * team_size; *dst_bytes = count * es; break;
     case 5 /* BSHMEM_COLL_FCOLLECT */: *src_bytes = count; *dst_bytes = count * team_size; break;
     case 6 /* BSHMEM_COLL_ALLTOALL */: *src_bytes = *dst_bytes = count * team_size; break;

@@ -32,6 +32,7 @@ __device__ int reduce_typed(const State& s, const DTeam& t, const CollArgs& a, i
   char* bulk = kDynSmem ? coll_dyn_smem : nullptr;
   T* d = reinterpret_cast<T*>(s.heap_base[s.my_pe] + a.dst_off);
   const T* src = reinterpret_cast<const T*>(s.heap_base[s.my_pe] + a.src_off);
+  if (a.kind == BSHMEM_COLL_REDUCE_ROOT) return coll::team_reduce_root<T>(s, t, a.op, d, src, a.n, a.root, cta, ncta, bulk);
   if (a.kind == BSHMEM_COLL_REDUCE_SCATTER) {
     if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value) {
       // large sums on the whole world: the switch reduces (see the allreduce below)
@@ -80,7 +81,7 @@ __device__ __noinline__ int run_coll(const State& s, DTeam t, const CollArgs& a,
       return coll::team_sync(s, t, cta);   // nobody overwrites a row that is still being read... by the next exchange
     }
 #endif
-    case BSHMEM_COLL_REDUCE: case BSHMEM_COLL_REDUCE_SCATTER:
+    case BSHMEM_COLL_REDUCE: case BSHMEM_COLL_REDUCE_SCATTER: case BSHMEM_COLL_REDUCE_ROOT:
       switch (a.dtype) {
 #define COLL_CASE(code, T) case code: return reduce_typed<T>(s, t, a, cta, ncta);
         COLL_TYPES(COLL_CASE)

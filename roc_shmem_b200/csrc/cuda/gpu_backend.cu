@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(128) k_rma_bulk(State s, char* dst, const char
 // which matters once the message is much larger than what the address-translation caches cover (132 CTAs on
 // 256 MiB lost 8 % with one contiguous share per CTA).
 constexpr uint64_t kRmaPiece = 256u << 10;
-__global__ void __launch_bounds__(1024) k_rma(State s, int pe, uint64_t sym_off, char* local, uint64_t n, int is_put, int scope) {
+__global__ void __launch_bounds__(512) k_rma(State s, int pe, uint64_t sym_off, char* local, uint64_t n, int is_put, int scope) {
   char* sym = s.heap_base[s.my_pe] + sym_off;
   // a message of up to grid x 256 KiB is still split evenly: every CTA gets one contiguous share
   uint64_t piece = ((n + gridDim.x - 1) / gridDim.x + 15) & ~15ull;
@@ -490,6 +490,10 @@ class GpuBackend final : public Backend {
     CollArgs a{}; a.kind = BSHMEM_COLL_REDUCE; a.dtype = dtype; a.op = op; a.dst_off = d; a.src_off = s; a.n = nelems;
     return launch(g, a, nelems * bshmem_dtype_size(dtype), "to_all");
   }
+  int reduce_root(const CollGroup& g, int dtype, int op, uint64_t d, uint64_t s, uint64_t nelems, int root) override {
+    CollArgs a{}; a.kind = BSHMEM_COLL_REDUCE_ROOT; a.dtype = dtype; a.op = op; a.dst_off = d; a.src_off = s; a.n = nelems; a.root = root;
+    return launch(g, a, nelems * bshmem_dtype_size(dtype), "reduce");
+  }
   int reduce_scatter(const CollGroup& g, int dtype, int op, uint64_t d, uint64_t s, uint64_t per_pe) override {
     CollArgs a{}; a.kind = BSHMEM_COLL_REDUCE_SCATTER; a.dtype = dtype; a.op = op; a.dst_off = d; a.src_off = s; a.n = per_pe;
     return launch(g, a, per_pe * bshmem_dtype_size(dtype) * g.size(), "reduce_scatter");
@@ -744,7 +748,7 @@ int bshmem_gpu_rma_kernel(bshmem_handle_t h, void* sym, void* local, uint64_t n,
   if (!h->to_offset(sym, n, &off) || pe < 0 || pe >= g->n_pes()) return BSHMEM_ERR_RANGE;
   if (ctas < 1) ctas = 1;
   if (threads < 32) threads = 32;
-  if (threads > 1024) threads = 1024;
+  if (threads > 512) threads = 512;     // the kernel's launch bound: eight 16-byte accesses in flight per thread need the registers
   // scope 3 = bulk async copies through shared memory
   const bool aligned = ((reinterpret_cast<uintptr_t>(local) | off | n) & 15) == 0;
   if (scope == 3 && !aligned) return BSHMEM_ERR_INVALID;

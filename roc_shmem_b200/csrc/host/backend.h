@@ -91,6 +91,7 @@ class Backend {
   virtual int sync(const CollGroup& g) = 0;
   virtual int broadcast(const CollGroup& g, uint64_t dst_off, uint64_t src_off, uint64_t nbytes, int root) = 0;
   virtual int reduce(const CollGroup& g, int dtype, int op, uint64_t dst_off, uint64_t src_off, uint64_t nelems) = 0;
+  virtual int reduce_root(const CollGroup& g, int dtype, int op, uint64_t dst_off, uint64_t src_off, uint64_t nelems, int root) = 0;
   virtual int reduce_scatter(const CollGroup& g, int dtype, int op, uint64_t dst_off, uint64_t src_off,
                              uint64_t nelems_per_pe) = 0;
   virtual int fcollect(const CollGroup& g, uint64_t dst_off, uint64_t src_off, uint64_t nbytes) = 0;

@@ -316,6 +316,18 @@ class CpuBackend final : public Backend {
     return BSHMEM_OK;
   }
 
+  int reduce_root(const CollGroup& g, int dtype, int op, uint64_t dst_off, uint64_t src_off, uint64_t nelems, int root) override {
+    int rc = sync(g);
+    if (rc != BSHMEM_OK) return rc;
+    uint64_t bytes = nelems * bshmem_dtype_size(dtype);
+    std::vector<char> tmp(g.my_idx == root ? bytes : 0);   // dest may alias source
+    if (g.my_idx == root && nelems) reduce_any(dtype, op, tmp.data(), sources(g, src_off), nelems);
+    rc = sync(g);       // the root has read every source
+    if (rc != BSHMEM_OK) return rc;
+    if (g.my_idx == root && bytes) memcpy(local_base() + dst_off, tmp.data(), bytes);
+    return BSHMEM_OK;
+  }
+
   int reduce_scatter(const CollGroup& g, int dtype, int op, uint64_t dst_off, uint64_t src_off, uint64_t per_pe) override {
     int rc = sync(g);
     if (rc != BSHMEM_OK) return rc;

@@ -591,6 +591,23 @@ int bshmem_team_reduce(bshmem_handle_t h, bshmem_team_t team, int dtype, int op,
   return reduce_impl(h, g, dtype, op, dest, src, nelems);
 }
 
+int bshmem_team_reduce_root(bshmem_handle_t h, bshmem_team_t team, int dtype, int op, void* dest, const void* src, size_t nelems,
+                            int root) {
+  CHECK_H(h);
+  CollGroup g;
+  int rc = h->group_of_team(team, &g);
+  if (rc != BSHMEM_OK) return h->fail(rc, "reduce: invalid team");
+  if (root < 0 || root >= g.size()) return h->fail(BSHMEM_ERR_INVALID, "reduce: root is not a member of the team");
+  size_t sz = bshmem_dtype_size(dtype);
+  if (!sz || op < BSHMEM_SUM || op > BSHMEM_XOR || (dtype >= BSHMEM_FLOAT && op >= BSHMEM_AND))
+    return h->fail(BSHMEM_ERR_INVALID, "reduce: bad dtype/op");
+  uint64_t doff, soff;
+  rc = coll_offsets(h, dest, nelems * sz, src, nelems * sz, &doff, &soff, "reduce");
+  if (rc != BSHMEM_OK) return rc;
+  h->global_stats.inc(ST_TO_ALL);
+  return note_timeout(h, h->backend->reduce_root(g, dtype, op, doff, soff, nelems, root), "reduce");
+}
+
 int bshmem_team_reduce_scatter(bshmem_handle_t h, bshmem_team_t team, int dtype, int op, void* dest, const void* src,
                                size_t nelems_per_pe) {
   CHECK_H(h);

@@ -122,6 +122,9 @@ int bshmem_team_broadcast(bshmem_handle_t h, bshmem_team_t team, void* dest, con
                           size_t nbytes, int root);
 int bshmem_team_reduce(bshmem_handle_t h, bshmem_team_t team, int dtype, int op, void* dest,
                        const void* src, size_t nelems);         /* allreduce */
+/* rooted reduce: only member `root` of the team receives op over all members' src (the others' dest is untouched) */
+int bshmem_team_reduce_root(bshmem_handle_t h, bshmem_team_t team, int dtype, int op, void* dest,
+                            const void* src, size_t nelems, int root);
 int bshmem_team_reduce_scatter(bshmem_handle_t h, bshmem_team_t team, int dtype, int op, void* dest,
                                const void* src, size_t nelems_per_pe);
 int bshmem_team_fcollect(bshmem_handle_t h, bshmem_team_t team, void* dest, const void* src, size_t nbytes);

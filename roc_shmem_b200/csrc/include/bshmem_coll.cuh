@@ -567,6 +567,26 @@ __device__ __forceinline__ int team_reduce(const State& s, const Team& t, int op
   return team_barrier(s, t, cta);         // results delivered; sources reusable
 }
 
+// rooted reduce: member `root` pulls every member's source and writes op over all of them into its dest; the other
+// members only take part in the entry sync (their source is ready) and the closing barrier (it has been read).
+// dest may alias source.  The reference offers only the `*_to_all` form (library/include/roc_shmem.hpp:837-887).
+template <typename T>
+__device__ __forceinline__ int team_reduce_root(const State& s, const Team& t, int op, T* dest, const T* source, size_t n, int root,
+                                                int cta = 0, int ncta = 1, char* bulk = nullptr) {
+  int rc = team_sync(s, t, cta);
+  if (rc != BSHMEM_OK) return rc;
+  if (t.my_idx == root) {
+    const T* srcs[BSHMEM_MAX_PES];
+    for (int k = 0; k < t.size; ++k) srcs[k] = dev::ptr(s, source, dev::team_pe(t, k));
+    size_t b, e;
+    split_range(n, ncta, cta, 16 / sizeof(T), &b, &e);
+    T* mine[1] = {dest};
+    reduce_range<T>(s, op, t.size, srcs, 1, mine, b, e, bulk);
+    if (cta == 0 && threadIdx.x == 0) { dev::stat(s, BSHMEM_DSTAT_COLL); dev::trace(s, BSHMEM_TRACE_COLL, s.my_pe, n * sizeof(T)); }
+  }
+  return team_barrier(s, t, cta);
+}
+
 // reduce-scatter: dest (n elements) = reduction of the members' source[my_idx*n : (my_idx+1)*n].
 template <typename T>
 __device__ __forceinline__ int team_reduce_scatter(const State& s, const Team& t, int op, T* dest, const T* source,

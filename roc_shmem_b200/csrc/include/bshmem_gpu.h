@@ -20,7 +20,8 @@ enum {
   BSHMEM_COLL_REDUCE_SCATTER = 4,
   BSHMEM_COLL_FCOLLECT = 5,
   BSHMEM_COLL_ALLTOALL = 6,
-  BSHMEM_COLL_EXCHANGE = 7
+  BSHMEM_COLL_EXCHANGE = 7,
+  BSHMEM_COLL_REDUCE_ROOT = 8
 };
 
 #ifdef __cplusplus

@@ -46,6 +46,7 @@ DSTAT_NAMES = ("put", "get", "put_signal", "p", "g", "amo", "fence", "quiet", "w
 TRACE_OPS = {1: "put", 2: "get", 3: "put_signal", 4: "amo", 5: "wait", 6: "barrier", 7: "coll", 8: "timeout"}
 
 COLL_SYNC, COLL_BARRIER, COLL_BROADCAST, COLL_REDUCE, COLL_REDUCE_SCATTER, COLL_FCOLLECT, COLL_ALLTOALL = range(7)
+COLL_REDUCE_ROOT = 8
 
 
 def cuda_lib() -> C.CDLL:

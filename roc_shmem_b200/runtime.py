@@ -362,6 +362,12 @@ class Runtime:
 
     to_all = reduce
 
+    def reduce_root(self, dest: torch.Tensor, src: torch.Tensor, root: int, op="sum", team=None) -> None:
+        """Rooted reduce: only member `root` of the team gets op over all members' `src` (the others' dest is untouched)."""
+        o = D.OPS[op] if isinstance(op, str) else int(op)
+        self._check(self.lib.bshmem_team_reduce_root(self.h, self._team(team), D.code_of(src.dtype), o, _ptr_of(dest),
+                                                     _ptr_of(src), src.numel(), root))
+
     def reduce_scatter(self, dest: torch.Tensor, src: torch.Tensor, op="sum", team=None) -> None:
         """dest (n elems) = op over members of their src[my_idx*n:(my_idx+1)*n]."""
         o = D.OPS[op] if isinstance(op, str) else int(op)

@@ -186,6 +186,36 @@ def test_broadcast_fcollect_alltoall_reduce_scatter():
     run_threads(4, body, heap_bytes=1 << 20)
 
 
+def test_rooted_reduce():
+    """Only the root's dest receives the reduction; a sub-team numbers its root relative to the team."""
+    def body(rt):
+        me, n = rt.my_pe, rt.n_pes
+        src = rt.empty((64,), torch.int32)
+        dst = rt.empty((64,), torch.int32)
+        src.copy_(torch.arange(64, dtype=torch.int32) + 10 * me)
+        dst.fill_(-7)
+        rt.reduce_root(dst, src, 2, "sum")
+        want = torch.arange(64, dtype=torch.int32) * n + 10 * sum(range(n))
+        assert torch.equal(dst, want) if me == 2 else bool((dst == -7).all())
+        rt.barrier_all()
+        rt.reduce_root(src, src, 0, "max")                           # in place on the root
+        if me == 0:
+            assert torch.equal(src, torch.arange(64, dtype=torch.int32) + 10 * (n - 1))
+        else:
+            assert torch.equal(src, torch.arange(64, dtype=torch.int32) + 10 * me)
+        rt.barrier_all()
+        odd = rt.team_world.split_strided(1, 2, n // 2)              # PEs 1, 3
+        f = rt.empty((8,), torch.float32)                            # symmetric allocations are collective over the world
+        g = rt.zeros((8,), torch.float32)
+        f.fill_(float(me))
+        if me % 2 == 1:
+            rt.reduce_root(g, f, 1, "sum", team=odd)                 # team member 1 = PE 3
+            assert bool((g == (4.0 if me == 3 else 0.0)).all())
+            with pytest.raises(shmem.ShmemError):
+                rt.reduce_root(g, f, 2, "sum", team=odd)             # not a member
+    run_threads(4, body, heap_bytes=1 << 20)
+
+
 def test_active_set_forms():
     def body(rt):
         me, n = rt.my_pe, rt.n_pes

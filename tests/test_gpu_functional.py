@@ -33,13 +33,6 @@ def test_every_type_single_pe(tester, name):
         assert all(r["latency_us"] > 0 for r in res["rows"]), res
 
 
-def test_type_table_matches_kernels():
-    from roc_shmem_b200.bench.functional import SPECS, lookup
-    ids = [s.id for s in SPECS]
-    assert ids == sorted(ids) and len(set(ids)) == len(ids) == 52 and 15 not in ids
-    assert lookup("2").name == "put" and lookup("wg_put_nbi").id == 31
-
-
 def test_bad_arguments_are_rejected(tester):
     from roc_shmem_b200 import ShmemError
     t = tester

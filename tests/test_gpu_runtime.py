@@ -195,6 +195,25 @@ def test_group_broadcast_fcollect_alltoall_reduce_scatter(group):
         assert torch.equal(rs_dst[i], acc)
 
 
+def test_group_rooted_reduce(group):
+    """Rooted reduce: the root's dest gets the float32 sum of every PE's source in PE order, the others stay as they were;
+    small (one block) and large (several blocks, bulk path) vectors."""
+    from roc_shmem_b200 import gpu
+    P = group.n_pes
+    for n, ctas in ((1000, 1), (3_000_000, 8)):
+        src = group.empty((n,), torch.float32)
+        dst = group.empty((n,), torch.float32)
+        for i in range(P):
+            src[i].copy_(torch.randn(n, device="cuda"))
+            dst[i].fill_(-3.0)
+        group.collective(gpu.COLL_REDUCE_ROOT, dst, src, n, dtype=torch.float32, op=0, root=1, ctas=ctas)
+        acc = src[0].clone()
+        for k in range(1, P):
+            acc = acc + src[k]
+        for i in range(P):
+            assert torch.equal(dst[i], acc) if i == 1 else bool((dst[i] == -3.0).all())
+
+
 def test_group_team_split_and_team_reduce(group):
     from roc_shmem_b200 import gpu
     slots = group.team_split(0, 0, 2, 2)                  # PEs {0, 2}
