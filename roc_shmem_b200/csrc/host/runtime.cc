@@ -57,7 +57,14 @@ int bshmem_runtime::fail(int code, const std::string& msg) {
 
 HostContext* bshmem_runtime::ctx(int idx) {
   if (idx < 0 || idx >= (int)ctxs.size() || !ctxs[idx] || !ctxs[idx]->live) return nullptr;
-  return ctxs[idx].get();
+  HostContext* c = ctxs[idx].get();
+  // PRIVATE: "used only by the thread that created it" (OpenSHMEM 1.5, 9.4.1).  Using it from another thread is a
+  // program error; with debug checks on, the call is refused instead of racing on the context's state.
+  if (cfg.debug && (c->options & BSHMEM_CTX_PRIVATE) && c->owner != std::this_thread::get_id()) {
+    fail(BSHMEM_ERR_STATE, "a PRIVATE context was used by a thread that did not create it");
+    return nullptr;
+  }
+  return c;
 }
 
 int bshmem_runtime::resolve_pe(int ctx_idx, int pe) {
@@ -296,6 +303,7 @@ int bshmem_team_create_ctx(bshmem_handle_t h, bshmem_team_t team, long options, 
       h->ctxs[i].reset(new HostContext());
       h->ctxs[i]->live = true;
       h->ctxs[i]->options = options;
+      h->ctxs[i]->owner = std::this_thread::get_id();
       h->ctxs[i]->team_slot = team;
       h->ctxs[i]->stats.enable(h->cfg.profile != 0);
       *out = (bshmem_ctx_t)i;

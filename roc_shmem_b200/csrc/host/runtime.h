@@ -10,6 +10,7 @@
 #pragma once
 #include <memory>
 #include <mutex>
+#include <thread>
 #include <string>
 #include <vector>
 
@@ -23,6 +24,7 @@ namespace bshmem {
 struct HostContext {
   bool live = false;
   long options = 0;
+  std::thread::id owner;  // creating thread: a BSHMEM_CTX_PRIVATE context is for that thread alone (checked in debug mode)
   int team_slot = 0;      // PEs passed with this ctx are relative to this team
   HostStats stats;
 };

@@ -62,6 +62,8 @@ typedef enum {
 #define BSHMEM_CTX_NOSTORE 1L     /* caller has no plain stores to publish  */
 #define BSHMEM_CTX_SERIALIZED 2L
 #define BSHMEM_CTX_WG_PRIVATE 4L  /* used by one thread block only          */
+#define BSHMEM_CTX_PRIVATE BSHMEM_CTX_WG_PRIVATE  /* host side: used only by the thread that created it (refused from
+                                                     any other thread when debug checks are on) */
 #define BSHMEM_CTX_SHARED 8L      /* shareable between blocks (locks on)    */
 
 /* ---- active-set scratch sizes (elements) -------------------------------- */

@@ -317,6 +317,39 @@ def test_contexts_many_and_team_relative():
     run_threads(4, body, heap_bytes=1 << 20)
 
 
+def test_private_context_is_refused_from_another_thread_in_debug_mode():
+    """CTX_PRIVATE promises use by the creating thread only; with debug checks on, another thread's call is refused
+    (without them it is the caller's responsibility, as in the specification)."""
+    import threading
+
+    def body(rt):
+        sym = rt.zeros((4,), torch.int32)
+        priv = rt.ctx_create(shmem.CTX_WG_PRIVATE)
+        ser = rt.ctx_create(shmem.CTX_SERIALIZED)
+        one = torch.tensor([7], dtype=torch.int32)
+        priv.put(sym[:1], one, rt.my_pe)                       # the creator may use it
+        seen = {}
+
+        def other():
+            try:
+                priv.put(sym[1:2], one, rt.my_pe)
+                seen["priv"] = "accepted"
+            except shmem.ShmemError as e:
+                seen["priv"] = "refused"
+            ser.put(sym[2:3], one, rt.my_pe)                   # SERIALIZED: any one thread at a time
+            ser.quiet()
+            seen["ser"] = "accepted"
+        t = threading.Thread(target=other)
+        t.start()
+        t.join()
+        priv.quiet()
+        assert seen == {"priv": "refused", "ser": "accepted"}
+        assert sym.tolist() == [7, 0, 7, 0]
+        priv.destroy()
+        ser.destroy()
+    run_threads(1, body, config=Config.from_env(backend="cpu", heap_bytes=1 << 20, debug=True))
+
+
 def test_malloc_semantics():
     def body(rt):
         assert rt.malloc(0) == 0                                   # malloc(0) -> null (collective)
