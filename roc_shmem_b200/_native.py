@@ -8,6 +8,7 @@ GPU code path never falls back to eager PyTorch when its library is missing.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 from pathlib import Path
 
@@ -23,17 +24,23 @@ class NativeLibraryMissing(ImportError):
 
 
 def load(name: str, *, build_if_missing: bool = True) -> C.CDLL:
-    """Load ``lib/<name>`` (building it first if its sources are newer)."""
+    """Load ``lib/<name>``.  An existing library is used as it is: a multi-rank job imports this module in every
+    rank at once, and ranks that each decided to recompile a library whose sources look newer would spend minutes
+    in the compiler, racing on the same object files, before the first collective.  A missing library is built
+    (one process at a time, under a file lock); set ``B200SHMEM_AUTO_REBUILD=1`` to also rebuild a stale one at
+    import, as a developer convenience on a single process.  ``python -m roc_shmem_b200.build`` is the build step."""
     with _lock:
         if name in _libs:
             return _libs[name]
         path = _LIB_DIR / name
-        if build_if_missing:
+        want_build = build_if_missing and (not path.exists() or os.environ.get("B200SHMEM_AUTO_REBUILD", "") == "1")
+        if want_build:
             try:
-                if name == "libbshmem_host.so":
-                    _build.build_host()
-                elif name in _build.CUDA_TARGETS:
-                    _build.build_cuda_target(name)
+                with _build_lock():
+                    if name == "libbshmem_host.so":
+                        _build.build_host()
+                    elif name in _build.CUDA_TARGETS:
+                        _build.build_cuda_target(name)
             except Exception as e:   # keep an existing binary usable if the rebuild fails
                 if not path.exists():
                     raise NativeLibraryMissing(f"cannot build {name}: {e}") from e
@@ -42,6 +49,23 @@ def load(name: str, *, build_if_missing: bool = True) -> C.CDLL:
         lib = C.CDLL(str(path), mode=C.RTLD_GLOBAL if name == "libbshmem_cuda.so" else C.RTLD_LOCAL)
         _libs[name] = lib
         return lib
+
+
+class _build_lock:
+    """Inter-process lock around an import-time build (ranks of one job share the source tree)."""
+
+    def __enter__(self):
+        import fcntl
+        _LIB_DIR.mkdir(exist_ok=True)
+        self._f = open(_LIB_DIR / ".build.lock", "w")
+        fcntl.flock(self._f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+        fcntl.flock(self._f, fcntl.LOCK_UN)
+        self._f.close()
+        return False
 
 
 class ErrorRecord(C.Structure):
