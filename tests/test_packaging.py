@@ -45,3 +45,21 @@ def test_api_reference_and_cmake_package(tmp_path):
     assert "bshmem::host" in cm and "bshmem::cuda" in cm
     out = subprocess.run([sys.executable, "-m", "roc_shmem_b200.pkgconfig", "--cflags", "--libs"], capture_output=True, text=True)
     assert "-lbshmem_host" in out.stdout and "csrc/include" in out.stdout
+
+
+def test_loader_uses_an_existing_library_without_rebuilding(monkeypatch):
+    """Every rank of a multi-rank job imports the package at the same time: an existing library must be loaded as it
+    is (no compiler run at import, even when a source file is newer), a missing one is built once under the lock, and
+    B200SHMEM_AUTO_REBUILD=1 brings the rebuild-at-import behaviour back for a developer."""
+    from roc_shmem_b200 import build
+    _native.host_lib()
+    calls = []
+    monkeypatch.setattr(build, "build_host", lambda *a, **k: calls.append("host"))
+    monkeypatch.setattr(_native, "_libs", {})
+    monkeypatch.delenv("B200SHMEM_AUTO_REBUILD", raising=False)
+    assert _native.load("libbshmem_host.so") is not None and calls == []
+    monkeypatch.setattr(_native, "_libs", {})
+    monkeypatch.setenv("B200SHMEM_AUTO_REBUILD", "1")
+    assert _native.load("libbshmem_host.so") is not None and calls == ["host"]
+    with _native._build_lock():                              # the lock file lives next to the libraries
+        assert (Path(_native._LIB_DIR) / ".build.lock").exists()
