@@ -186,6 +186,49 @@ def test_broadcast_fcollect_alltoall_reduce_scatter():
     run_threads(4, body, heap_bytes=1 << 20)
 
 
+def test_collectives_with_eight_and_sixteen_pes():
+    """The host runtime at the PE counts of a full node: world collectives, a strided team of every other PE and a
+    team-relative context, with 8 and with 16 (= BSHMEM_MAX_PES) PEs."""
+    def body(rt):
+        me, n = rt.my_pe, rt.n_pes
+        src = rt.empty((33,), torch.int64)
+        src.fill_(me + 1)
+        big = rt.empty((33 * n,), torch.int64)
+        rt.fcollect(big, src)
+        assert big.view(n, 33)[:, 7].tolist() == [p + 1 for p in range(n)]
+        a_src = rt.empty((33 * n,), torch.int64)
+        for j in range(n):
+            a_src[j * 33:(j + 1) * 33] = (me << 16) + j
+        rt.alltoall(big, a_src)
+        assert big.view(n, 33)[:, 0].tolist() == [(j << 16) + me for j in range(n)]
+        acc = rt.empty((33,), torch.int64)
+        rt.reduce(acc, src, "sum")
+        assert bool((acc == n * (n + 1) // 2).all())
+        rt.reduce_scatter(acc, a_src, "max")
+        assert bool((acc == ((n - 1) << 16) + me).all())
+        acc.fill_(-1)
+        rt.reduce_root(acc, src, n - 1, "sum")
+        assert bool((acc == (n * (n + 1) // 2 if me == n - 1 else -1)).all())
+        rt.barrier_all()
+        even = rt.team_split_strided(None, 0, 2, n // 2)
+        if even.valid:
+            assert even.n_pes == n // 2 and even.my_pe == me // 2
+        f = rt.empty((4,), torch.float32)
+        g = rt.zeros((4,), torch.float32)
+        f.fill_(float(me))
+        if even.valid:
+            rt.reduce(g, f, "sum", team=even)
+            assert bool((g == float(sum(range(0, n, 2)))).all())
+            with rt.ctx_create(0, even) as c:
+                c.put(g[:1], torch.tensor([1000.0 + me]), (even.my_pe + 1) % even.n_pes)   # team-relative neighbour
+            even.sync()
+            assert float(g[0]) == 1000.0 + (me - 2) % n
+            even.destroy()
+        rt.barrier_all()
+    run_threads(8, body, heap_bytes=1 << 20)
+    run_threads(16, body, heap_bytes=1 << 20)
+
+
 def test_rooted_reduce():
     """Only the root's dest receives the reduction; a sub-team numbers its root relative to the team."""
     def body(rt):
