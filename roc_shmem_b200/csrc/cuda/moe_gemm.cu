@@ -347,10 +347,9 @@ int bshmem_moe_grouped_gemm_tn(const void* A, const void* B, void* C, int G, int
   p.a_blocks_per_group = M / BM;
   p.k_rows_per_group = cap;
   p.group_m = 16;
-  // CTA pairs unless the single-CTA loop is asked for (B200SHMEM_TN_SINGLE, kept for comparison): a CTA then loads
-  // two 64-wide column blocks per operand and stage instead of four
-  static const bool single = getenv("B200SHMEM_TN_SINGLE") != nullptr;
-  const bool pair = !single && g_pairs[dev] > 0;
+  // CTA pairs (a CTA then loads two 64-wide column blocks per operand and stage instead of four); the single-CTA loop
+  // only if the device cannot hold a pair of this kernel
+  const bool pair = g_pairs[dev] > 0;
   const uint32_t blocks = pair ? 2 : 4;
   // preferred: one 3-D copy per operand and stage; if the driver refuses that view, boxes of 64 MN-elements
   // (128 bytes, the swizzle span) by 64 tokens, one per column block
