@@ -48,24 +48,70 @@ def reference_arm(args) -> int:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power draw and the clock-event (throttle) reasons of one GPU while the timed region runs:
+    read-only NVML queries from a thread every 20 ms, or `nvidia-smi -lms 100` if the NVML binding is not there.
+    Nothing is set or reset."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    # NVML clock-event reason bits
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, nvml=None, bus_id=None):
         self.index = index
         self.proc = None
         self.lines: list[str] = []
+        self.samples: list[tuple[float, float, int]] = []      # (sm MHz, watts, reason mask)
+        self.max_mhz = None
+        self._nvml = nvml                                      # injectable for tests
+        self._bus_id = bus_id
+        self._stop = threading.Event()
+        self.thread = None
+        self.mode = None
+
+    def _start_nvml(self) -> bool:
+        try:
+            nv = self._nvml
+            if nv is None:
+                import pynvml as nv
+            nv.nvmlInit()
+            bus = self._bus_id
+            if bus is None:
+                import torch
+                pr = torch.cuda.get_device_properties(self.index)
+                bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+            h = nv.nvmlDeviceGetHandleByPciBusId(bus.encode() if isinstance(bus, str) else bus)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            reasons_fn(h)
+            nv.nvmlDeviceGetPowerUsage(h)
+        except Exception:
+            return False
+
+        def poll() -> None:
+            while not self._stop.is_set():
+                try:
+                    self.samples.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
+                                         nv.nvmlDeviceGetPowerUsage(h) / 1000.0, int(reasons_fn(h))))
+                except Exception:
+                    pass
+                self._stop.wait(0.02)
+        self.thread = threading.Thread(target=poll, daemon=True)
+        self.thread.start()
+        self.mode = "nvml"
+        return True
 
     def start(self) -> None:
+        if self._start_nvml():
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
+            self.mode = "nvidia-smi"
         except OSError:
             self.proc = None
 
@@ -73,9 +119,24 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    @staticmethod
+    def _summary(sm, mx, power, reasons, mode) -> dict:
+        loaded = [c for c, p in zip(sm, power) if p > 400.0] or sm
+        return {"sm_mhz": statistics.median(loaded) if loaded else None, "sm_max_mhz": mx,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "samples_under_load": len(loaded),
+                "reasons": sorted(reasons), "sampler": mode}
+
     def stop(self) -> dict:
+        if self.mode == "nvml":
+            self._stop.set()
+            self.thread.join(timeout=2)
+            mask = 0
+            for _, _, m in self.samples:
+                mask |= m
+            reasons = {name for name, bit in self.REASON_BITS.items() if mask & bit}
+            return self._summary([s[0] for s in self.samples], self.max_mhz, [s[1] for s in self.samples], reasons, "nvml, 20 ms")
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML binding and no nvidia-smi"]}
         time.sleep(0.15)
         self.proc.terminate()       # the exact process started above
         try:
@@ -94,10 +155,7 @@ class ClockSampler:
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        loaded = [c for c, p in zip(sm, power) if p > 400.0] or sm
-        return {"sm_mhz": statistics.median(loaded) if loaded else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "samples_under_load": len(loaded),
-                "reasons": sorted(reasons)}
+        return self._summary(sm, max(mx) if mx else None, power, reasons, "nvidia-smi -lms 100")
 
 
 def main() -> int:
