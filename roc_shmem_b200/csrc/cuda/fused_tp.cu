@@ -62,22 +62,29 @@ struct GemmRs : PolicyDefaults {
   // First every tile whose rows another PE owns: in sub-round s every rank visits the owners me+1, me+2, ...,
   // me-1 and computes row-block s of each, so the P ranks always send to P different owners.  Then the tiles of
   // this PE's own rows, whose epilogue adds the P-1 partials that arrived meanwhile and writes the result.
-  // Tile order.  First the tiles of rows that other PEs own, then this PE's own rows.  Row blocks are taken in groups
-  // of up to kGroupM; inside a group the owner changes slowest (step s: every rank sends to owner me+1+s, so the P
-  // ranks always send to P different owners), then the column block, and the row block of the group fastest: the CTA
-  // pairs that run side by side share a few A row blocks and a few B column blocks, which keeps both in L2.
-  static constexpr int kGroupM = 8;
+  // Tile order.  First the tiles of rows that other PEs own, then this PE's own rows.  Row blocks are taken in groups;
+  // inside a group the owner changes slowest (step s: every rank sends to owner me+1+s, so the P ranks always send to
+  // P different owners), then the column block, and the row block of the group fastest: the CTA pairs that run side by
+  // side share a few A row blocks and a few B column blocks, which keeps both in L2.  A group is at most 8 row blocks
+  // and at most half of an owner's rows, so there are at least two groups: the partials of a PE's first group have all
+  // been sent by the time the senders start their second one, long before the PE's own tiles (same group order) need
+  // them.
+  __device__ static __forceinline__ int group_rows(int bpo) {
+    const int half = bpo >> 1;
+    return half < 1 ? 1 : (half > 8 ? 8 : half);
+  }
   __device__ static __forceinline__ void tile_coords(const Params& p, int tile, int* m_blk, int* n_blk) {
     const int num_n = p.core.num_n_blocks;
     const int bpo = p.blocks_per_owner;
+    const int gm = group_rows(bpo);
     const int send_tiles = (p.P - 1) * bpo * num_n;
     int t = tile, owners = p.P - 1;
     const bool own = tile >= send_tiles;
     if (own) { t = tile - send_tiles; owners = 1; }
-    const int per_group = owners * kGroupM * num_n;          // only the last group can be smaller
+    const int per_group = owners * gm * num_n;               // only the last group can be smaller
     const int sg = t / per_group;
-    const int first = sg * kGroupM;
-    const int rows = min(kGroupM, bpo - first);
+    const int first = sg * gm;
+    const int rows = min(gm, bpo - first);
     const int rem = t - sg * per_group;
     const int per_step = rows * num_n;
     const int step = rem / per_step, r2 = rem - step * per_step;
