@@ -539,6 +539,7 @@ __device__ __forceinline__ int ctx_n_pes(const Ctx& c) { return c.team.size; }
 __device__ __forceinline__ void ctx_fence(const State& s, const Ctx&) { fence(s); }
 __device__ __forceinline__ void ctx_fence(const State& s, const Ctx& c, int pe) { fence_pe(s, ctx_pe(c, pe)); }
 __device__ __forceinline__ void ctx_quiet(const State& s, const Ctx&) { quiet(s); }
+__device__ __forceinline__ void ctx_threadfence_system(const State&, const Ctx&) { threadfence_system(); }
 template <typename T> __device__ __forceinline__ T* ctx_ptr(const State& s, const Ctx& c, const T* local, int pe) { return ptr(s, local, ctx_pe(c, pe)); }
 
 template <Scope S = THREAD>

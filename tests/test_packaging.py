@@ -63,3 +63,24 @@ def test_loader_uses_an_existing_library_without_rebuilding(monkeypatch):
     assert _native.load("libbshmem_host.so") is not None and calls == ["host"]
     with _native._build_lock():                              # the lock file lives next to the libraries
         assert (Path(_native._LIB_DIR) / ".build.lock").exists()
+
+
+def test_porting_guide_targets_exist():
+    """Every name the porting guide sends a ROC_SHMEM user to is declared in a public header or is an attribute of the
+    Python classes, and the guide covers the reference header's untyped entry points."""
+    import re
+
+    import roc_shmem_b200 as shmem
+    from roc_shmem_b200.runtime import Context, Runtime, Team
+    assert docs.porting_targets_missing() == []
+    classes = {"Runtime": Runtime, "Context": Context, "Team": Team}
+    for ref, (_host, _dev, py, _note) in docs.PORTING.items():
+        for cls, attr in re.findall(r"(Runtime|Context|Team)\.(\w+)", py):
+            assert hasattr(classes[cls], attr) or attr in ("my_pe", "n_pes", "team"), (ref, cls, attr)
+        for attr in re.findall(r"roc_shmem_b200\.(\w+)", py):
+            assert hasattr(shmem, attr), (ref, attr)
+    for must in ("init", "finalize", "malloc", "putmem", "getmem_nbi", "ctx_create", "wg_init", "wg_team_create_ctx",
+                 "ctx_wg_team_sync", "team_split_strided", "barrier_all", "ptr", "timer", "global_exit"):
+        assert must in docs.PORTING
+    text = docs.porting_guide()
+    assert "| `putmem` |" in text and "Typed families" in text
