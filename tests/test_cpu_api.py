@@ -219,6 +219,7 @@ def test_collectives_with_eight_and_sixteen_pes():
         if even.valid:
             rt.reduce(g, f, "sum", team=even)
             assert bool((g == float(sum(range(0, n, 2)))).all())
+            even.sync()                                        # every member has its result before anyone overwrites g[0]
             with rt.ctx_create(0, even) as c:
                 c.put(g[:1], torch.tensor([1000.0 + me]), (even.my_pe + 1) % even.n_pes)   # team-relative neighbour
             even.sync()
