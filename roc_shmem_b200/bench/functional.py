@@ -82,6 +82,8 @@ def lookup(algo: str) -> Spec:
 class Tester:
     """Buffers and the per-size protocol.  Construction allocates symmetric memory: every PE must build it."""
 
+    __test__ = False      # not a pytest class, whatever its name says
+
     def __init__(self, rt, max_size: int, wgs: int, wg_size: int, loop: int = 100, skip: int = 10, loop_large: int = 25,
                  large: int = 32768, ctx_options: int = 0):
         self.rt, self.max_size, self.wgs, self.wg_size = rt, max_size, wgs, wg_size
