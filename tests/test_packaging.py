@@ -84,3 +84,54 @@ def test_porting_guide_targets_exist():
         assert must in docs.PORTING
     text = docs.porting_guide()
     assert "| `putmem` |" in text and "Typed families" in text
+
+
+def test_cmake_build_install_and_consumer(tmp_path):
+    """The repository's CMakeLists.txt builds the host library (BSHMEM_CUDA=OFF keeps the test short; the CUDA targets
+    use the same file), installs headers + library + package files, and a consumer project finds the installed
+    package with find_package(bshmem) and runs."""
+    import shutil
+    if shutil.which("cmake") is None:
+        import pytest
+        pytest.skip("cmake is not installed")
+    root = Path(__file__).resolve().parents[1]
+    build, prefix = tmp_path / "build", tmp_path / "prefix"
+    for cmd in (["cmake", "-S", str(root), "-B", str(build), "-DBSHMEM_CUDA=OFF"],
+                ["cmake", "--build", str(build), "-j", "8"],
+                ["cmake", "--install", str(build), "--prefix", str(prefix)]):
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert (prefix / "include" / "bshmem" / "bshmem.h").exists() and (prefix / "include" / "bshmem" / "bshmem_device.cuh").exists()
+    app = tmp_path / "app"
+    app.mkdir()
+    (app / "CMakeLists.txt").write_text(textwrap.dedent("""
+        cmake_minimum_required(VERSION 3.24)
+        project(app LANGUAGES C CXX)
+        find_package(bshmem REQUIRED)
+        add_executable(app app.c)
+        target_link_libraries(app PRIVATE bshmem::bshmem_host)
+        """))
+    (app / "app.c").write_text(textwrap.dedent("""
+        #include <stdio.h>
+        #include "bshmem.h"
+        int main(void) {
+          void* world = 0; bshmem_handle_t h = 0;
+          if (bshmem_cpu_world_create(0, 1, 1 << 20, &world) != BSHMEM_OK) return 1;
+          if (bshmem_cpu_init(world, 0, 0, &h) != BSHMEM_OK) return 2;
+          int* x = (int*)bshmem_malloc(h, 4 * sizeof(int));
+          int r = -1;
+          x[0] = 5;
+          if (bshmem_team_reduce_root(h, BSHMEM_TEAM_WORLD, BSHMEM_INT32, BSHMEM_SUM, &x[1], &x[0], 1, 0) != BSHMEM_OK) return 3;
+          r = x[1];
+          bshmem_free(h, x);
+          bshmem_finalize(h);
+          bshmem_cpu_world_destroy(world);
+          printf("CMAKE_CONSUMER_OK %d\\n", r);
+          return r == 5 ? 0 : 4;
+        }"""))
+    r = subprocess.run(["cmake", "-S", str(app), "-B", str(app / "b"), f"-DCMAKE_PREFIX_PATH={prefix}"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    r = subprocess.run(["cmake", "--build", str(app / "b")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    r = subprocess.run([str(app / "b" / "app")], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "CMAKE_CONSUMER_OK 5" in r.stdout, r.stdout + r.stderr
