@@ -55,6 +55,21 @@ def test_bootstrap_allgather_barrier_broadcast_and_fd_exchange():
         assert texts == ["from-0", "from-1", "from-2"]        # each descriptor really is the peer's pipe
 
 
+def test_bootstrap_with_eight_ranks():
+    """The rank count of a full node: every rank serves its descriptor to seven peers while it collects theirs."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "store")
+        procs = [ctx.Process(target=_boot_worker, args=(r, 8, path, q)) for r in range(8)]
+        [p.start() for p in procs]
+        res = sorted(q.get(timeout=180) for _ in range(8))
+        [p.join(30) for p in procs]
+    for rank, ranks, root, texts in res:
+        assert ranks == list(range(8)) and root == "hello"
+        assert texts == [f"from-{p}" for p in range(8)]
+
+
 def test_bootstrap_barrier_times_out_when_a_rank_never_joins():
     b = Bootstrap(dist.HashStore(), 0, 2, timeout_s=0.3)
     with pytest.raises(TimeoutError):
