@@ -205,6 +205,7 @@ def main() -> int:
     def timed_blocks(step_fn) -> list[float]:
         """ms per step of each timed block of `steps` steps (max over ranks); blocks repeat until MIN_TIMED_S."""
         it = 0
+        barrier()          # ranks enter the first (untimed) step together: the kernels' waits on peers are bounded
         for _ in range(warmup):
             step_fn(it); it += 1
         blocks, total_ms = [], 0.0
