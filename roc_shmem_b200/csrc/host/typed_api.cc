@@ -46,7 +46,11 @@ int bshmem_quiet(void) { return bshmem_ctx_quiet(cur(), BSHMEM_CTX_DEFAULT); }
   int bshmem_##N##_test(T* ivar, int cmp, T v) { int r = 0; bshmem_test(cur(), D, ivar, cmp, bits(v), &r); return r; } \
   int bshmem_##N##_broadcast(bshmem_team_t t, T* d, const T* s, size_t n, int root) { return bshmem_team_broadcast(cur(), t, d, s, n * sizeof(T), root); } \
   int bshmem_##N##_fcollect(bshmem_team_t t, T* d, const T* s, size_t n) { return bshmem_team_fcollect(cur(), t, d, s, n * sizeof(T)); } \
-  int bshmem_##N##_alltoall(bshmem_team_t t, T* d, const T* s, size_t n) { return bshmem_team_alltoall(cur(), t, d, s, n * sizeof(T)); }
+  int bshmem_##N##_alltoall(bshmem_team_t t, T* d, const T* s, size_t n) { return bshmem_team_alltoall(cur(), t, d, s, n * sizeof(T)); } \
+  int bshmem_ctx_##N##_put_signal(bshmem_ctx_t c, T* d, const T* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe) { return bshmem_ctx_putmem_signal(cur(), c, d, s, n * sizeof(T), sig, v, op, pe); } \
+  int bshmem_ctx_##N##_put_signal_nbi(bshmem_ctx_t c, T* d, const T* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe) { return bshmem_ctx_putmem_signal_nbi(cur(), c, d, s, n * sizeof(T), sig, v, op, pe); } \
+  int bshmem_##N##_put_signal(T* d, const T* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe) { return bshmem_ctx_##N##_put_signal(BSHMEM_CTX_DEFAULT, d, s, n, sig, v, op, pe); } \
+  int bshmem_##N##_put_signal_nbi(T* d, const T* s, size_t n, uint64_t* sig, uint64_t v, int op, int pe) { return bshmem_ctx_##N##_put_signal_nbi(BSHMEM_CTX_DEFAULT, d, s, n, sig, v, op, pe); }
 BSHMEM_RMA_TYPES(DEF_RMA)
 
 #define DEF_AMO_STD(T, N, D)                                                                                        \

@@ -115,7 +115,12 @@ int bshmem_quiet(void);
   int bshmem_##N##_test(T* ivar, int cmp, T value);                                           \
   int bshmem_##N##_broadcast(bshmem_team_t team, T* dest, const T* src, size_t nelems, int root); \
   int bshmem_##N##_fcollect(bshmem_team_t team, T* dest, const T* src, size_t nelems);        \
-  int bshmem_##N##_alltoall(bshmem_team_t team, T* dest, const T* src, size_t nelems);
+  int bshmem_##N##_alltoall(bshmem_team_t team, T* dest, const T* src, size_t nelems);        \
+  /* put-with-signal, OpenSHMEM 1.5 (not in the reference): the signal update is visible after the data */ \
+  int bshmem_##N##_put_signal(T* dest, const T* src, size_t nelems, uint64_t* sig_addr, uint64_t signal, int sig_op, int pe);     \
+  int bshmem_##N##_put_signal_nbi(T* dest, const T* src, size_t nelems, uint64_t* sig_addr, uint64_t signal, int sig_op, int pe); \
+  int bshmem_ctx_##N##_put_signal(bshmem_ctx_t c, T* dest, const T* src, size_t nelems, uint64_t* sig_addr, uint64_t signal, int sig_op, int pe); \
+  int bshmem_ctx_##N##_put_signal_nbi(bshmem_ctx_t c, T* dest, const T* src, size_t nelems, uint64_t* sig_addr, uint64_t signal, int sig_op, int pe);
 BSHMEM_RMA_TYPES(BSHMEM_DECL_RMA)
 #undef BSHMEM_DECL_RMA
 

@@ -145,7 +145,8 @@ PORTING_FAMILIES = [
      "coll::[ctx_]wg_to_all<T>, coll::team_reduce / team_reduce_root / team_reduce_scatter<T>"),
     ("roc_shmem_[ctx_]TYPE_wg_broadcast / alltoall / fcollect", "bshmem_TYPE_broadcast / alltoall / fcollect, bshmem_team_*",
      "coll::[ctx_]wg_broadcast / wg_alltoall / wg_fcollect<T>"),
-    ("— (not in the reference)", "bshmem_putmem_signal, bshmem_signal_fetch", "dev::[ctx_]putmem_signal<Scope>, dev::signal_fetch"),
+    ("— (not in the reference; OpenSHMEM 1.5)", "bshmem_[ctx_]putmem_signal[_nbi], bshmem_[ctx_]TYPE_put_signal[_nbi], bshmem_signal_fetch",
+     "dev::[ctx_]putmem_signal<Scope>, dev::signal_fetch"),
 ]
 
 

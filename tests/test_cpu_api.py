@@ -463,6 +463,20 @@ def test_typed_c_api_through_ctypes():
         assert bool((fo == float(n)).all())
         assert lib.bshmem_int_wait_until(ints.data_ptr(), 3, ((me - 1) % n) * 10) == 0       # GE
         rt.barrier_all()
+        # typed put-with-signal (OpenSHMEM 1.5 names): the neighbour sees the data once its signal word counts 1
+        lib.bshmem_float_put_signal.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_uint64, C.c_int, C.c_int]
+        lib.bshmem_ctx_float_put_signal_nbi.argtypes = [C.c_int32] + lib.bshmem_float_put_signal.argtypes
+        lib.bshmem_uint64_wait_until.argtypes = [C.c_void_p, C.c_int, C.c_uint64]
+        sig = rt.zeros((2,), torch.int64)
+        vals = (C.c_float * 16)(*[me + 0.5] * 16)
+        assert lib.bshmem_float_put_signal(fo.data_ptr(), C.addressof(vals), 16, sig.data_ptr(), 1, 1, (me + 1) % n) == 0
+        assert lib.bshmem_uint64_wait_until(sig.data_ptr(), 3, 1) == 0                      # GE 1
+        assert bool((fo == (me - 1) % n + 0.5).all())
+        assert lib.bshmem_ctx_float_put_signal_nbi(0, fl.data_ptr(), C.addressof(vals), 16, sig[1:].data_ptr(), 7, 0,
+                                                   (me + 1) % n) == 0
+        assert lib.bshmem_uint64_wait_until(sig[1:].data_ptr(), 0, 7) == 0                  # EQ 7
+        assert bool((fl == (me - 1) % n + 0.5).all())
+        rt.barrier_all()
     run_threads(2, body, heap_bytes=1 << 20)
 
 
