@@ -128,3 +128,47 @@ class Bootstrap:
         srv.close()
         self.barrier(tag + "-done")
         return got
+
+
+class ExitWatcher:
+    """Job-wide abort over the bootstrap store: the counterpart of the reference's roc_shmem_global_exit, which calls
+    MPI_Abort (library/src/roc_shmem.cpp).  `raise_exit(status)` publishes the status; a daemon thread in every other
+    rank polls the key (non-blocking `check`, every `period_s`) and calls `on_exit(status)` — by default it prints one
+    line and ends the process with that status, whatever its main thread is blocked in.  Store errors (the store's
+    host has gone at shutdown) end the watcher silently."""
+
+    KEY = "global-exit"
+
+    def __init__(self, boot: "Bootstrap", on_exit=None, period_s: float = 0.2):
+        import threading
+        self.boot, self.period_s = boot, period_s
+        self.on_exit = on_exit or self._default_exit
+        self._stop = threading.Event()
+        self._raised = False
+        self.thread = threading.Thread(target=self._run, name="bshmem-exit-watcher", daemon=True)
+        self.thread.start()
+
+    def _default_exit(self, status: int) -> None:
+        import sys
+        print(f"[bshmem pe {self.boot.rank}] global_exit({status}) was called by another PE: leaving", file=sys.stderr, flush=True)
+        os._exit(status & 0xFF)
+
+    def _run(self) -> None:
+        while not self._stop.wait(self.period_s):
+            try:
+                if self.boot.store.check([self.KEY]):
+                    status = int(pickle.loads(self.boot.store.get(self.KEY)))
+                    if not self._raised:
+                        self.on_exit(status)
+                    return
+            except Exception:
+                return
+
+    def raise_exit(self, status: int) -> None:
+        """Publish the job's exit status (first caller wins is not needed: every value ends the job)."""
+        self._raised = True
+        self.boot.store.set(self.KEY, pickle.dumps(int(status)))
+
+    def stop(self) -> None:
+        self._stop.set()
+

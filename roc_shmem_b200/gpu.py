@@ -295,6 +295,21 @@ class DeviceRuntime(Runtime):
         out = res.tolist()
         return out[:out.index(-1)]
 
+    def global_exit(self, status: int = 0) -> None:
+        """End the whole job with `status` (the reference calls MPI_Abort): publish the status in the bootstrap store —
+        every other rank's watcher thread ends its process with it — and leave this process the same way."""
+        w = getattr(self, "_exit_watcher", None)
+        if w is not None:
+            w.raise_exit(status)
+        self.lib.bshmem_global_exit(self.h, int(status))
+        os._exit(int(status) & 0xFF)
+
+    def finalize(self) -> None:
+        w = getattr(self, "_exit_watcher", None)
+        if w is not None:
+            w.stop()
+        super().finalize()
+
     def functional_run(self, test_type: int, *, size: int, wgs: int, wg_size: int, loops: int, skip: int, peer: int, sym_a, sym_b,
                        local, words, timers, status, team=None, ctx_options: int = 0, initiator: bool = True,
                        n_bins: int = 0) -> float:
@@ -387,6 +402,8 @@ def init_device_runtime(boot: Bootstrap, cfg: Config, device: Optional[int] = No
         rt.set_nvls(True)
     if n > 1:
         boot.barrier("gpu-init")
+        from .bootstrap import ExitWatcher
+        rt._exit_watcher = ExitWatcher(boot)       # global_exit of any PE ends every PE
     if proxy:
         from .proxy import attach_proxy
         attach_proxy(rt)

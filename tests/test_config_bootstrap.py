@@ -6,7 +6,7 @@ import tempfile
 import pytest
 import torch.distributed as dist
 
-from roc_shmem_b200.bootstrap import Bootstrap
+from roc_shmem_b200.bootstrap import Bootstrap, ExitWatcher
 from roc_shmem_b200.config import Config
 
 
@@ -74,3 +74,47 @@ def test_bootstrap_barrier_times_out_when_a_rank_never_joins():
     b = Bootstrap(dist.HashStore(), 0, 2, timeout_s=0.3)
     with pytest.raises(TimeoutError):
         b.barrier()
+
+
+def test_exit_watcher_delivers_the_status_to_every_other_rank():
+    """global_exit over the store: the caller publishes a status; every other rank's watcher thread hands it to its
+    exit hook (here a recorder instead of os._exit), and a stopped watcher stays silent."""
+    import time
+    store = dist.HashStore()
+    ranks = [Bootstrap(store, r, 3, timeout_s=5) for r in range(3)]
+    seen = {}
+    watchers = [ExitWatcher(b, on_exit=lambda st, r=b.rank: seen.setdefault(r, st), period_s=0.01) for b in ranks]
+    time.sleep(0.05)
+    assert seen == {}
+    watchers[2].stop()                       # rank 2 has finalised: it must not react any more
+    time.sleep(0.05)
+    watchers[1].raise_exit(42)
+    deadline = time.time() + 5
+    while 0 not in seen and time.time() < deadline:
+        time.sleep(0.01)
+    time.sleep(0.05)
+    assert seen == {0: 42}                   # not the caller (it leaves by itself), not the stopped one
+    for w in watchers:
+        w.stop()
+
+
+def _exit_worker(rank, world, path):
+    import time
+    b = Bootstrap(dist.FileStore(path, world), rank, world, timeout_s=30)
+    w = ExitWatcher(b, period_s=0.02)
+    b.barrier()
+    if rank == 1:
+        w.raise_exit(9)
+        os._exit(9)
+    time.sleep(30)                           # a blocked main thread: only the watcher can end this process
+    os._exit(0)
+
+
+def test_global_exit_ends_blocked_processes_with_the_status():
+    ctx = mp.get_context("spawn")
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "store")
+        procs = [ctx.Process(target=_exit_worker, args=(r, 3, path)) for r in range(3)]
+        [p.start() for p in procs]
+        [p.join(25) for p in procs]
+        assert [p.exitcode for p in procs] == [9, 9, 9]
