@@ -170,5 +170,9 @@ class ExitWatcher:
         self.boot.store.set(self.KEY, pickle.dumps(int(status)))
 
     def stop(self) -> None:
+        """Ends the watcher (joined, so no store call is in flight when the interpreter or the store goes away)."""
+        import threading
         self._stop.set()
+        if threading.current_thread() is not self.thread:
+            self.thread.join(timeout=2.0)
 
